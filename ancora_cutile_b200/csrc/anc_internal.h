@@ -1,0 +1,80 @@
+// Internal declarations shared by the translation units of libancora_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include "../../include/ancora_b200.h"
+
+struct anc_ctx {
+  int device;
+  cudaStream_t stream;
+  bool own_stream;
+  uint32_t *d_status;       // device status word: kernels OR error bits into it
+  void *d_work;             // small device workspace (Frobenius partial sums)
+  size_t work_bytes;
+  void *d_flush;            // L2 flush buffer, allocated on first use
+  size_t flush_bytes;
+  int sm_count;
+};
+
+// entries of the device tables the Muon plan builds for the group launches
+struct anc_mom_entry { float *buf; const void *g; int slot, K, N, tr; };
+struct anc_upd_entry { float *p32; uint16_t *p16; int slot, K, N, tr; };
+
+// device status bits
+#define ANC_DEV_TIMEOUT_TMA 0x1u     // producer/consumer mbarrier wait ran out
+#define ANC_DEV_TIMEOUT_MMA 0x2u
+#define ANC_DEV_TIMEOUT_EPI 0x4u
+#define ANC_DEV_BAD_INDEX 0x8u       // a table index failed its bounds check
+
+void anc_set_error(const char *fmt, ...);
+int anc_cuda_fail(cudaError_t e, const char *what);
+
+#define ANC_CUDA(call)                                           \
+  do {                                                           \
+    cudaError_t _e = (call);                                     \
+    if (_e != cudaSuccess) return anc_cuda_fail(_e, #call);      \
+  } while (0)
+
+#define ANC_REQUIRE(cond, ...)                                   \
+  do {                                                           \
+    if (!(cond)) {                                               \
+      anc_set_error(__VA_ARGS__);                                \
+      return ANC_E_INVALID;                                      \
+    }                                                            \
+  } while (0)
+
+static inline cudaStream_t anc_pick_stream(anc_ctx *ctx, void *stream) {
+  return stream ? (cudaStream_t)stream : ctx->stream;
+}
+
+struct anc_device_guard {
+  int prev;
+  bool changed;
+  explicit anc_device_guard(int dev) : prev(-1), changed(false) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
+      changed = (cudaSetDevice(dev) == cudaSuccess);
+    }
+  }
+  ~anc_device_guard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+// ---- launchers implemented in the kernel translation units -----------------
+int anc_launch_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u, int K,
+                        int N, float momentum, int nesterov, int transposed, cudaStream_t st);
+int anc_launch_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O, int K, int N,
+                      float lr_scale, int transposed, cudaStream_t st);
+int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
+                             cudaStream_t st);
+int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
+                              int elems_per_w, int grad_dtype, float momentum, int nesterov,
+                              cudaStream_t st);
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *obase, int n_w,
+                            int elems_per_w, float lr_scale_wide, float lr_scale_tall,
+                            cudaStream_t st);
+int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
+                       int E, int M, int N, float alpha, float beta, cudaStream_t st);
+void anc_gemm_cache_destroy(anc_ctx *ctx);

@@ -1,0 +1,391 @@
+// Muon's elementwise kernels for sm_100a (HBM-bound sweeps):
+//   momentum + Nesterov  -> packed bf16 Newton-Schulz input   (12 B/elem, bf16 grad)
+//   Frobenius normalise  -> fixed-order two-level reduction, then scale in place
+//   master update + bf16 refresh                               (12 B/elem)
+// Arithmetic follows ancora/kernels/muon_ns.py:184-186 (nb = mu*b + g;
+// u = RNE(g + mu*nb)) and :227-229 (pn = p - lr_scale*O; p16 = RNE(pn)) with
+// separately rounded float32 operations, so results equal a numpy float32
+// evaluation bit for bit.  Tall weights (K > N) store u transposed / read O
+// transposed through a shared-memory tile, which is bit-identical to the untransposed
+// kernel followed by a transpose (reference: _muon_mom_t, _muon_update_cast_t).
+#include <cuda_bf16.h>
+#include "anc_internal.h"
+
+namespace {
+
+constexpr int kTile = 64;
+constexpr int kThreads = 256;
+constexpr int kPad = 8;   // row pitch 72 bf16 = 144 B: 16-byte aligned rows, few bank conflicts
+
+// Table entries.  `slot` selects the weight's matrix inside the packed Newton-Schulz
+// operand: slot s starts at element s * K * N and holds (K,N) if !tr, else (N,K).
+struct MomW {
+  float *buf;
+  const void *g;
+  int slot, K, N, tr;
+};
+
+struct UpdW {
+  float *p32;
+  uint16_t *p16;
+  int slot, K, N, tr;
+};
+
+__device__ __forceinline__ uint32_t rne16(float x) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ float bf16_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// One 64x64 tile of one weight.  Thread t: columns 4*(t%16)..+3, rows t/16 + 16*k.
+template <bool kGradF32>
+__device__ __forceinline__ void momentum_tile(const MomW &w, uint16_t *xbase, int ti, int tj, float mu,
+                                              int nesterov, uint16_t (*sm)[kTile + kPad]) {
+  uint16_t *wx = xbase + (size_t)w.slot * w.K * w.N;
+  const int c4 = (threadIdx.x & 15) * 4;
+  const int r0 = threadIdx.x >> 4;
+  const int col = tj * kTile + c4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int rl = r0 + 16 * k;
+    const size_t idx = (size_t)(ti * kTile + rl) * w.N + col;
+    const float4 b = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx));
+    float g[4];
+    if constexpr (kGradF32) {
+      const float4 gv = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx));
+      g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+    } else {
+      const uint2 gv = __ldcs(reinterpret_cast<const uint2 *>((const uint16_t *)w.g + idx));
+      g[0] = __uint_as_float(gv.x << 16); g[1] = __uint_as_float(gv.x & 0xFFFF0000u);
+      g[2] = __uint_as_float(gv.y << 16); g[3] = __uint_as_float(gv.y & 0xFFFF0000u);
+    }
+    const float bb[4] = {b.x, b.y, b.z, b.w};
+    float nb[4];
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      nb[j] = __fadd_rn(__fmul_rn(mu, bb[j]), g[j]);
+      const float u = nesterov ? __fadd_rn(g[j], __fmul_rn(mu, nb[j])) : nb[j];
+      h[j] = rne16(u);
+    }
+    __stcs(reinterpret_cast<float4 *>(w.buf + idx), make_float4(nb[0], nb[1], nb[2], nb[3]));
+    if (!w.tr) {
+      *reinterpret_cast<uint2 *>(wx + idx) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    } else {
+      *reinterpret_cast<uint2 *>(&sm[rl][c4]) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    }
+  }
+  if (w.tr) {
+    __syncthreads();
+    // output tile: rows = source columns, cols = source rows.  Thread: row t/4, 16 elems.
+    const int oc = threadIdx.x >> 2;
+    const int rr = (threadIdx.x & 3) * 16;
+    uint32_t pk[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      pk[j] = (uint32_t)sm[rr + 2 * j][oc] | ((uint32_t)sm[rr + 2 * j + 1][oc] << 16);
+    uint16_t *dst = wx + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+    reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void update_tile(const UpdW &w, const uint16_t *obase, float lr_scale,
+                                            int ti, int tj, uint16_t (*sm)[kTile + kPad]) {
+  const uint16_t *wo = obase + (size_t)w.slot * w.K * w.N;
+  const int c4 = (threadIdx.x & 15) * 4;
+  const int r0 = threadIdx.x >> 4;
+  const int col = tj * kTile + c4;
+  if (w.tr) {
+    // stage O^T tile: source rows = columns of the weight tile
+    const int oc = threadIdx.x >> 2;
+    const int rr = (threadIdx.x & 3) * 16;
+    const uint16_t *src = wo + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+    const uint4 a = reinterpret_cast<const uint4 *>(src)[0];
+    const uint4 b = reinterpret_cast<const uint4 *>(src)[1];
+    reinterpret_cast<uint4 *>(&sm[oc][rr])[0] = a;
+    reinterpret_cast<uint4 *>(&sm[oc][rr])[1] = b;
+    __syncthreads();
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int rl = r0 + 16 * k;
+    const size_t idx = (size_t)(ti * kTile + rl) * w.N + col;
+    const float4 p = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
+    float o[4];
+    if (!w.tr) {
+      const uint2 ov = *reinterpret_cast<const uint2 *>(wo + idx);
+      o[0] = __uint_as_float(ov.x << 16); o[1] = __uint_as_float(ov.x & 0xFFFF0000u);
+      o[2] = __uint_as_float(ov.y << 16); o[3] = __uint_as_float(ov.y & 0xFFFF0000u);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = bf16_f32(sm[c4 + j][rl]);
+    }
+    const float pp[4] = {p.x, p.y, p.z, p.w};
+    float pn[4];
+    uint32_t h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pn[j] = __fsub_rn(pp[j], __fmul_rn(lr_scale, o[j]));
+      h[j] = rne16(pn[j]);
+    }
+    __stcs(reinterpret_cast<float4 *>(w.p32 + idx), make_float4(pn[0], pn[1], pn[2], pn[3]));
+    *reinterpret_cast<uint2 *>(w.p16 + idx) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  }
+  if (w.tr) __syncthreads();
+}
+
+// Table-driven launches: every weight in the table has the same K*N, hence the same
+// number of tiles (tiles_per_w); block b works on weight b / tiles_per_w.
+template <bool kGradF32>
+__global__ void __launch_bounds__(kThreads)
+momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int tiles_per_w, float mu,
+                int nesterov) {
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  const int total = n_w * tiles_per_w;
+  for (int b = blockIdx.x; b < total; b += gridDim.x) {
+    const int wi = b / tiles_per_w;
+    const int t = b - wi * tiles_per_w;
+    const MomW w = table[wi];
+    const int tn = w.N / kTile;
+    momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+  }
+}
+
+// lr_scale_wide applies to weights stored with K <= N, lr_scale_tall to K > N
+// (lr * sqrt(max(1, K/N)), ancora/optim/muon.py:101,176).
+__global__ void __launch_bounds__(kThreads)
+update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, int tiles_per_w,
+              float lr_scale_wide, float lr_scale_tall) {
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  const int total = n_w * tiles_per_w;
+  for (int b = blockIdx.x; b < total; b += gridDim.x) {
+    const int wi = b / tiles_per_w;
+    const int t = b - wi * tiles_per_w;
+    const UpdW w = table[wi];
+    const int tn = w.N / kTile;
+    update_tile(w, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm);
+  }
+}
+
+// single-weight forms (table passed by value)
+template <bool kGradF32>
+__global__ void __launch_bounds__(kThreads)
+momentum_one_kernel(MomW w, uint16_t *xbase, float mu, int nesterov) {
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  const int tn = w.N / kTile;
+  const int total = (w.K / kTile) * tn;
+  for (int t = blockIdx.x; t < total; t += gridDim.x)
+    momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+}
+
+__global__ void __launch_bounds__(kThreads)
+update_one_kernel(UpdW w, const uint16_t *obase, float lr_scale) {
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  const int tn = w.N / kTile;
+  const int total = (w.K / kTile) * tn;
+  for (int t = blockIdx.x; t < total; t += gridDim.x)
+    update_tile(w, obase, lr_scale, t / tn, t % tn, sm);
+}
+
+// ---- Frobenius normalisation ------------------------------------------------
+// Each matrix is cut into blocks of kFroBlock contiguous elements.  Level 1: one
+// CTA per block; a thread adds its 64 squares in index order, a warp combines with a
+// xor-shuffle tree, warp 0 adds the 8 warp sums in order.  Level 2 (inside the scale
+// kernel): the per-block sums of one matrix are added by one warp, lane-strided then
+// the same shuffle tree.  The order never depends on the grid or on which other
+// matrices share the launch.
+constexpr int kFroBlock = 16384;
+
+__device__ __forceinline__ float warp_tree_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+fro_partial_kernel(const uint16_t *__restrict__ X, float *__restrict__ partial, int total_blocks) {
+  __shared__ float wsum[kThreads / 32];
+  for (int b = blockIdx.x; b < total_blocks; b += gridDim.x) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(X + (size_t)b * kFroBlock);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < kFroBlock / (kThreads * 8); ++k) {
+      const uint4 r = src[k * kThreads + threadIdx.x];
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+        acc = __fadd_rn(acc, __fmul_rn(lo, lo));
+        acc = __fadd_rn(acc, __fmul_rn(hi, hi));
+      }
+    }
+    acc = warp_tree_sum(acc);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = wsum[0];
+#pragma unroll
+      for (int k = 1; k < kThreads / 32; ++k) s = __fadd_rn(s, wsum[k]);
+      partial[b] = s;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fro_scale_kernel(uint16_t *__restrict__ X, const float *__restrict__ partial,
+                 float *__restrict__ recip, int blocks_per_matrix, int total_blocks, float eps) {
+  __shared__ float s_r;
+  for (int b = blockIdx.x; b < total_blocks; b += gridDim.x) {
+    const int e = b / blocks_per_matrix;
+    if (threadIdx.x < 32) {
+      const float *pp = partial + (size_t)e * blocks_per_matrix;
+      float acc = 0.f;
+      for (int k = threadIdx.x; k < blocks_per_matrix; k += 32) acc = __fadd_rn(acc, pp[k]);
+      acc = warp_tree_sum(acc);
+      if (threadIdx.x == 0) {
+        const float r = __fdiv_rn(1.0f, __fadd_rn(__fsqrt_rn(acc), eps));
+        s_r = r;
+        if (b - e * blocks_per_matrix == 0) recip[e] = r;
+      }
+    }
+    __syncthreads();
+    const float r = s_r;
+    uint4 *dst = reinterpret_cast<uint4 *>(X + (size_t)b * kFroBlock);
+#pragma unroll
+    for (int k = 0; k < kFroBlock / (kThreads * 8); ++k) {
+      uint4 v = dst[k * kThreads + threadIdx.x];
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __fmul_rn(__uint_as_float(w[j] << 16), r);
+        const float hi = __fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), r);
+        w[j] = rne16(lo) | (rne16(hi) << 16);
+      }
+      dst[k * kThreads + threadIdx.x] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+// ---- launchers -----------------------------------------------------------------
+
+static int check_shape(int K, int N) {
+  ANC_REQUIRE(K > 0 && N > 0 && K % 64 == 0 && N % 64 == 0,
+              "Muon weight (%d,%d) tile-misaligned: K and N must be multiples of 64", K, N);
+  return ANC_OK;
+}
+
+int anc_launch_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u, int K,
+                        int N, float momentum, int nesterov, int transposed, cudaStream_t st) {
+  int rc = check_shape(K, N);
+  if (rc) return rc;
+  MomW w = {buf, g, 0, K, N, transposed ? 1 : 0};
+  int tiles = (K / kTile) * (N / kTile);
+  int grid = tiles < ctx->sm_count * 8 ? tiles : ctx->sm_count * 8;
+  if (grad_dtype == ANC_GRAD_F32)
+    momentum_one_kernel<true><<<grid, kThreads, 0, st>>>(w, u, momentum, nesterov);
+  else
+    momentum_one_kernel<false><<<grid, kThreads, 0, st>>>(w, u, momentum, nesterov);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+int anc_launch_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O, int K, int N,
+                      float lr_scale, int transposed, cudaStream_t st) {
+  int rc = check_shape(K, N);
+  if (rc) return rc;
+  UpdW w = {p32, p16, 0, K, N, transposed ? 1 : 0};
+  int tiles = (K / kTile) * (N / kTile);
+  int grid = tiles < ctx->sm_count * 8 ? tiles : ctx->sm_count * 8;
+  update_one_kernel<<<grid, kThreads, 0, st>>>(w, O, lr_scale);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
+                             cudaStream_t st) {
+  ANC_REQUIRE(E > 0 && M > 0 && N > 0, "bad shape");
+  ANC_REQUIRE(((size_t)M * N) % kFroBlock == 0, "matrix of %dx%d elements is not a multiple of %d",
+              M, N, kFroBlock);
+  const int bpm = (int)(((size_t)M * N) / kFroBlock);
+  const size_t total = (size_t)E * bpm;
+  ANC_REQUIRE(total < (1u << 30), "too many blocks");
+  if (total * sizeof(float) > ctx->work_bytes) {
+    ANC_CUDA(cudaStreamSynchronize(st));
+    ANC_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->d_work) cudaFree(ctx->d_work);
+    ctx->d_work = nullptr;
+    ctx->work_bytes = total * sizeof(float) * 2;
+    ANC_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
+  }
+  int grid = (int)(total < (size_t)ctx->sm_count * 8 ? total : (size_t)ctx->sm_count * 8);
+  fro_partial_kernel<<<grid, kThreads, 0, st>>>(X, (float *)ctx->d_work, (int)total);
+  ANC_CUDA(cudaGetLastError());
+  fro_scale_kernel<<<grid, kThreads, 0, st>>>(X, (const float *)ctx->d_work, recip, bpm, (int)total,
+                                              eps);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+// Table-driven group launches used by the Muon plan.
+static_assert(sizeof(anc_mom_entry) == sizeof(MomW), "table layout");
+static_assert(sizeof(anc_upd_entry) == sizeof(UpdW), "table layout");
+
+int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
+                              int elems_per_w, int grad_dtype, float momentum, int nesterov,
+                              cudaStream_t st) {
+  const int tpw = elems_per_w / (kTile * kTile);
+  const long long total = (long long)n_w * tpw;
+  int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
+  if (grid == 0) return ANC_OK;
+  if (grad_dtype == ANC_GRAD_F32)
+    momentum_kernel<true><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov);
+  else
+    momentum_kernel<false><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *obase, int n_w,
+                            int elems_per_w, float lr_scale_wide, float lr_scale_tall,
+                            cudaStream_t st) {
+  const int tpw = elems_per_w / (kTile * kTile);
+  const long long total = (long long)n_w * tpw;
+  int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
+  if (grid == 0) return ANC_OK;
+  update_kernel<<<grid, kThreads, 0, st>>>((const UpdW *)d_table, obase, n_w, tpw, lr_scale_wide,
+                                            lr_scale_tall);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+extern "C" {
+
+int anc_muon_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u, int K,
+                      int N, float momentum, int nesterov, int transposed, void *stream) {
+  ANC_REQUIRE(ctx && buf && g && u, "NULL argument");
+  anc_device_guard guard(ctx->device);
+  return anc_launch_momentum(ctx, buf, g, grad_dtype, u, K, N, momentum, nesterov, transposed,
+                             anc_pick_stream(ctx, stream));
+}
+
+int anc_muon_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O, int K, int N,
+                    float lr_scale, int transposed, void *stream) {
+  ANC_REQUIRE(ctx && p32 && p16 && O, "NULL argument");
+  anc_device_guard guard(ctx->device);
+  return anc_launch_update(ctx, p32, p16, O, K, N, lr_scale, transposed,
+                           anc_pick_stream(ctx, stream));
+}
+
+int anc_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
+                      void *stream) {
+  ANC_REQUIRE(ctx && X && recip, "NULL argument");
+  anc_device_guard guard(ctx->device);
+  return anc_launch_fro_normalize(ctx, X, recip, E, M, N, eps, anc_pick_stream(ctx, stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,273 @@
+// Host orchestration of the batched Muon step: groups weights by Newton-Schulz
+// shape, owns the packed bf16 scratch and issues, per group,
+//   momentum (1 launch) -> Frobenius normalise (2) -> ns_steps x 3 GEMM phases -> update (1)
+// on the caller's stream, with no host synchronisation.  This is the role of
+// BatchedProjMuon / ResidentMuon / the expert branch of GroupedMoEFFN.step in the
+// reference (ancora/optim/muon.py:180-201,256-277; ancora/kernels/moe.py:578-588),
+// except that a whole shape group is batched at once: a B200 has the HBM for it and
+// the GEMM kernel's tile scheduler needs thousands of tiles to fill 148 SMs.
+#include <algorithm>
+#include <map>
+#include <math.h>
+#include <vector>
+#include "anc_internal.h"
+
+namespace {
+
+struct Group {
+  int M, Nn;                       // Newton-Schulz orientation, M <= Nn
+  std::vector<int> widx;           // plan weight indices, in registration order
+  anc_mom_entry *d_mom = nullptr;  // device tables, one entry per weight
+  anc_upd_entry *d_upd = nullptr;
+  double scale_tall = 1.0;         // sqrt(max(1, K/N)) for the K > N members
+};
+
+struct TimedSpan {
+  int phase;
+  cudaEvent_t a, b;
+};
+
+}  // namespace
+
+struct anc_muon_plan {
+  anc_ctx *ctx;
+  int grad_dtype;
+  int max_batch;
+  std::vector<anc_muon_weight> weights;   // owned weights only
+  std::vector<Group> groups;
+  uint16_t *X = nullptr, *Y = nullptr, *A = nullptr, *B = nullptr;
+  float *recip = nullptr;
+  uint64_t scratch_bytes = 0;
+  bool timing = false;
+  std::vector<TimedSpan> spans;
+  double last_flops = 0.0;
+  int last_launches = 0;
+};
+
+static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16_t *&Y, int E, int M,
+                    int N, int steps, const float *coeffs, cudaStream_t st) {
+  for (int k = 0; k < steps; ++k) {
+    const float a = coeffs[3 * k], b = coeffs[3 * k + 1], c = coeffs[3 * k + 2];
+    int rc = anc_launch_ns_gemm(ctx, 0, X, nullptr, A, E, M, N, 0.f, 1.f, st);
+    if (rc) return rc;
+    rc = anc_launch_ns_gemm(ctx, 1, A, nullptr, B, E, M, N, b, c, st);
+    if (rc) return rc;
+    rc = anc_launch_ns_gemm(ctx, 2, B, X, Y, E, M, N, a, 1.f, st);
+    if (rc) return rc;
+    std::swap(X, Y);
+  }
+  return ANC_OK;
+}
+
+static void plan_free(anc_muon_plan *pl) {
+  for (auto &g : pl->groups) {
+    if (g.d_mom) cudaFree(g.d_mom);
+    if (g.d_upd) cudaFree(g.d_upd);
+  }
+  for (void *p : {(void *)pl->X, (void *)pl->Y, (void *)pl->A, (void *)pl->B, (void *)pl->recip})
+    if (p) cudaFree(p);
+  for (auto &s : pl->spans) {
+    cudaEventDestroy(s.a);
+    cudaEventDestroy(s.b);
+  }
+  delete pl;
+}
+
+extern "C" {
+
+int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_weights, int grad_dtype,
+                         int my_rank, int max_batch, anc_muon_plan **out) {
+  ANC_REQUIRE(ctx && out && (weights || n_weights == 0), "NULL argument");
+  ANC_REQUIRE(grad_dtype == ANC_GRAD_BF16 || grad_dtype == ANC_GRAD_F32, "bad grad_dtype");
+  *out = nullptr;
+  anc_device_guard guard(ctx->device);
+  anc_muon_plan *pl = new anc_muon_plan();
+  pl->ctx = ctx;
+  pl->grad_dtype = grad_dtype;
+  pl->max_batch = max_batch;
+  std::map<std::pair<int, int>, int> gindex;
+  for (int i = 0; i < n_weights; ++i) {
+    const anc_muon_weight &w = weights[i];
+    if (w.owner >= 0 && w.owner != my_rank) continue;
+    if (!w.buf || !w.g || !w.p32 || !w.p16) {
+      anc_set_error("Muon weight %d has a NULL pointer", i);
+      plan_free(pl);
+      return ANC_E_INVALID;
+    }
+    if (w.K <= 0 || w.N <= 0 || w.K % 128 || w.N % 128) {
+      anc_set_error("Muon weight (%d,%d) tile-misaligned: K and N must be multiples of 128", w.K, w.N);
+      plan_free(pl);
+      return ANC_E_INVALID;
+    }
+    const int M = std::min(w.K, w.N), Nn = std::max(w.K, w.N);
+    auto key = std::make_pair(M, Nn);
+    auto it = gindex.find(key);
+    if (it == gindex.end()) {
+      gindex[key] = (int)pl->groups.size();
+      Group g;
+      g.M = M;
+      g.Nn = Nn;
+      g.scale_tall = pow((double)Nn / (double)M, 0.5);   // Python's max(1, K/N) ** 0.5
+      pl->groups.push_back(g);
+      it = gindex.find(key);
+    }
+    pl->groups[it->second].widx.push_back((int)pl->weights.size());
+    pl->weights.push_back(w);
+  }
+  // scratch: sized for the largest batch over all groups
+  size_t xe = 0, ae = 0, emax = 0;
+  for (auto &g : pl->groups) {
+    const size_t E = pl->max_batch > 0 ? std::min<size_t>(pl->max_batch, g.widx.size()) : g.widx.size();
+    xe = std::max(xe, E * (size_t)g.M * g.Nn);
+    ae = std::max(ae, E * (size_t)g.M * g.M);
+    emax = std::max(emax, E);
+    std::vector<anc_mom_entry> mom;
+    std::vector<anc_upd_entry> upd;
+    for (size_t s = 0; s < g.widx.size(); ++s) {
+      const anc_muon_weight &w = pl->weights[g.widx[s]];
+      const int slot = (int)(s % E);
+      mom.push_back({w.buf, w.g, slot, w.K, w.N, w.K > w.N ? 1 : 0});
+      upd.push_back({w.p32, w.p16, slot, w.K, w.N, w.K > w.N ? 1 : 0});
+    }
+    cudaError_t e = cudaMalloc((void **)&g.d_mom, mom.size() * sizeof(anc_mom_entry));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&g.d_upd, upd.size() * sizeof(anc_upd_entry));
+    if (e == cudaSuccess)
+      e = cudaMemcpy(g.d_mom, mom.data(), mom.size() * sizeof(anc_mom_entry), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+      e = cudaMemcpy(g.d_upd, upd.data(), upd.size() * sizeof(anc_upd_entry), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      plan_free(pl);
+      return anc_cuda_fail(e, "muon tables");
+    }
+  }
+  if (xe) {
+    cudaError_t e = cudaMalloc((void **)&pl->X, xe * 2);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->Y, xe * 2);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->A, ae * 2);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->B, ae * 2);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->recip, emax * sizeof(float));
+    if (e != cudaSuccess) {
+      plan_free(pl);
+      return anc_cuda_fail(e, "muon scratch");
+    }
+    pl->scratch_bytes = 4 * xe + 4 * ae + emax * sizeof(float);
+  }
+  *out = pl;
+  return ANC_OK;
+}
+
+int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, int ns_steps,
+                  const float *coeffs, float eps, void *stream) {
+  ANC_REQUIRE(pl && (coeffs || ns_steps == 0), "NULL argument");
+  ANC_REQUIRE(ns_steps >= 0 && ns_steps <= 64, "bad ns_steps %d", ns_steps);
+  anc_ctx *ctx = pl->ctx;
+  anc_device_guard guard(ctx->device);
+  cudaStream_t st = anc_pick_stream(ctx, stream);
+  for (auto &s : pl->spans) {
+    cudaEventDestroy(s.a);
+    cudaEventDestroy(s.b);
+  }
+  pl->spans.clear();
+  pl->last_flops = 0.0;
+  pl->last_launches = 0;
+  auto begin_span = [&](int phase) {
+    if (!pl->timing) return;
+    TimedSpan sp;
+    sp.phase = phase;
+    cudaEventCreate(&sp.a);
+    cudaEventCreate(&sp.b);
+    cudaEventRecord(sp.a, st);
+    pl->spans.push_back(sp);
+  };
+  auto end_span = [&]() {
+    if (!pl->timing) return;
+    cudaEventRecord(pl->spans.back().b, st);
+  };
+  for (auto &g : pl->groups) {
+    const int total = (int)g.widx.size();
+    const int cap = pl->max_batch > 0 ? std::min(pl->max_batch, total) : total;
+    const int epw = g.M * g.Nn;
+    // lr * sqrt(max(1, K/N)) in double, then one float32 rounding (ancora/optim/muon.py:176,200)
+    const float scale_wide = (float)(lr * 1.0);
+    const float scale_tall = (float)(lr * g.scale_tall);
+    for (int w0 = 0; w0 < total; w0 += cap) {
+      const int E = std::min(cap, total - w0);
+      uint16_t *X = pl->X, *Y = pl->Y;
+      begin_span(0);
+      int rc = anc_launch_momentum_group(ctx, g.d_mom + w0, X, E, epw, pl->grad_dtype, momentum,
+                                         nesterov, st);
+      end_span();
+      if (rc) return rc;
+      begin_span(1);
+      rc = anc_launch_fro_normalize(ctx, X, pl->recip, E, g.M, g.Nn, eps, st);
+      end_span();
+      if (rc) return rc;
+      begin_span(2);
+      rc = ns_chain(ctx, X, pl->A, pl->B, Y, E, g.M, g.Nn, ns_steps, coeffs, st);
+      end_span();
+      if (rc) return rc;
+      pl->last_flops += (double)E * ns_steps *
+                        (4.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M);
+      pl->last_launches += 3 * ns_steps;
+      begin_span(3);
+      rc = anc_launch_update_group(ctx, g.d_upd + w0, X, E, epw, scale_wide, scale_tall, st);
+      end_span();
+      if (rc) return rc;
+    }
+  }
+  return ANC_OK;
+}
+
+int anc_muon_plan_set_timing(anc_muon_plan *pl, int on) {
+  ANC_REQUIRE(pl, "plan is NULL");
+  pl->timing = on != 0;
+  return ANC_OK;
+}
+
+int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double *ns_flops, int *ns_launches) {
+  ANC_REQUIRE(pl && ms, "NULL argument");
+  anc_device_guard guard(pl->ctx->device);
+  for (int i = 0; i < 4; ++i) ms[i] = 0.f;
+  for (auto &s : pl->spans) {
+    ANC_CUDA(cudaEventSynchronize(s.b));
+    float t = 0.f;
+    ANC_CUDA(cudaEventElapsedTime(&t, s.a, s.b));
+    ms[s.phase] += t;
+  }
+  if (ns_flops) *ns_flops = pl->last_flops;
+  if (ns_launches) *ns_launches = pl->last_launches;
+  return ANC_OK;
+}
+
+int anc_muon_plan_scratch_bytes(anc_muon_plan *pl, uint64_t *bytes) {
+  ANC_REQUIRE(pl && bytes, "NULL argument");
+  *bytes = pl->scratch_bytes;
+  return ANC_OK;
+}
+
+int anc_muon_plan_destroy(anc_muon_plan *pl) {
+  if (!pl) return ANC_OK;
+  anc_device_guard guard(pl->ctx->device);
+  cudaStreamSynchronize(pl->ctx->stream);
+  plan_free(pl);
+  return ANC_OK;
+}
+
+int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y, float *recip,
+                   int E, int M, int N, int steps, const float *coeffs, float eps, void *stream) {
+  ANC_REQUIRE(ctx && X && A && B && Y && recip && (coeffs || steps == 0), "NULL argument");
+  ANC_REQUIRE(M <= N, "Newton-Schulz needs M <= N (got %d x %d); transpose tall weights first", M, N);
+  ANC_REQUIRE(M % 128 == 0 && N % 128 == 0, "NS shape (%d,%d) must be multiples of 128", M, N);
+  anc_device_guard guard(ctx->device);
+  cudaStream_t st = anc_pick_stream(ctx, stream);
+  int rc = anc_launch_fro_normalize(ctx, X, recip, E, M, N, eps, st);
+  if (rc) return rc;
+  uint16_t *x = X, *y = Y;
+  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, st);
+  if (rc) return rc;
+  if (x != X)   // odd number of steps: result sits in Y, copy it home (muon_ns.py:274-276)
+    ANC_CUDA(cudaMemcpyAsync(X, x, (size_t)E * M * N * 2, cudaMemcpyDeviceToDevice, st));
+  return ANC_OK;
+}
+
+}  // extern "C"

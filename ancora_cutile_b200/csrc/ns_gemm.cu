@@ -1,0 +1,512 @@
+// Batched Newton-Schulz GEMM phases for sm_100a: bf16 operands staged in shared
+// memory by TMA, tcgen05.mma with fp32 accumulators in tensor memory (TMEM), fused
+// axpy + bf16 rounding in the epilogue.  One persistent CTA per SM walks a static
+// tile list; the accumulator is double-buffered in TMEM so the epilogue of one tile
+// overlaps the MMAs of the next.
+//
+//   mode 0 (gram)  : C = RNE(P P^T)                    lower 128-blocks + mirrored store
+//   mode 1 (poly)  : C = RNE(alpha*P + beta*(P P^T))   P symmetric, so P P^T = P P
+//   mode 2 (apply) : C = RNE(alpha*Q + beta*(P Q))     full tiles, Q read N-major
+//
+// which are the three launches per iteration of the reference's fused chain
+// (ancora/kernels/muon_ns.py:261-273: _gemm_nt_tril+_mirror, _gemm_axpy_tril+_mirror,
+// _gemm_axpy_bf16).  Every output element is produced by exactly one tile with a
+// fixed K order (no split-K, no atomics), so results are bitwise independent of the
+// grid and of which other matrices share the launch.
+//
+// All waits are bounded: a wait that runs out records a status bit, raises a CTA-wide
+// abort flag and the kernel drains and returns (TMEM is always released).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <map>
+#include <vector>
+#include "anc_internal.h"
+
+namespace {
+
+constexpr int BM = 128;            // tile rows (UMMA M)
+constexpr int BK = 64;             // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;          // 16 KiB
+constexpr int kBBytes = 256 * BK * 2;         // 32 KiB (tile width up to 256)
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct GemmParams {
+  const uint16_t *D;      // axpy operand (modes 1, 2), same layout as C
+  uint16_t *C;
+  const uint32_t *tile_tab;
+  uint32_t *status;
+  int E, M, ldc;          // matrices, rows per matrix, row pitch of C/D in elements
+  int tiles_per_matrix, total_tiles, kblocks, mode;
+  float alpha, beta;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if (it > 64) {
+      __nanosleep(128);
+      if ((it & 255) == 0 && *abort_flag) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte
+// offsets (all >> 4), version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) |
+         ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;             // stage buffers, 1024-aligned
+  uint8_t *gen_base = smem_raw + (base - raw);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(gen_base + kStages * kStageBytes);
+  const uint32_t bar0 = base + kStages * kStageBytes;
+  // barrier slots: full[0..S), empty[S..2S), tmem_full[2S..2S+2), tmem_empty[2S+2..2S+4)
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // TMEM allocation: one full warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const bool nmajor_b = (p.mode == 2);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+        const int e = t / p.tiles_per_matrix;
+        const uint32_t tt = p.tile_tab[t - e * p.tiles_per_matrix];
+        const int i = tt & 0xFF, j = (tt >> 8) & 0xFF, w = (tt >> 16) & 0xFF;
+        const int row0 = e * p.M;
+        const uint32_t bytes = kABytes + (uint32_t)w * 128u * BK * 2u;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+            atomicOr(p.status, ANC_DEV_TIMEOUT_TMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t sa = base + s * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+          mbar_expect_tx(full_bar(s), bytes);
+          tma_load_2d(sa, &tmA, kb * BK, row0 + i * BM, full_bar(s));
+          if (!nmajor_b) {
+            // K-major B operand: 128-row boxes of P, rows (j + h) * 128
+            for (int h = 0; h < w; ++h)
+              tma_load_2d(sb + h * (128 * BK * 2), &tmB, kb * BK, row0 + (j + h) * 128, full_bar(s));
+          } else {
+            // N-major B operand: boxes of 64 columns x 64 K-rows of Q
+            for (int c = 0; c < 2 * w; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &tmB, j * 128 + c * 64, row0 + kb * BK, full_bar(s));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++acc_it) {
+        const int e = t / p.tiles_per_matrix;
+        const uint32_t tt = p.tile_tab[t - e * p.tiles_per_matrix];
+        const int w = (tt >> 16) & 0xFF;
+        const uint32_t n_dim = (uint32_t)w * 128u;
+        // instruction descriptor: D=f32, A=B=bf16, A K-major, B K- or N-major, N, M=128
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((nmajor_b ? 1u : 0u) << 16) |
+                               ((n_dim >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        const uint32_t buf = acc_it & 1;
+        const uint32_t aph = (acc_it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) {
+          atomicOr(p.status, ANC_DEV_TIMEOUT_MMA);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 256u;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+            atomicOr(p.status, ANC_DEV_TIMEOUT_MMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // A: K-major, 8-row groups 1024 B apart; K advance = 32 B inside the swizzle row
+            const uint64_t da = make_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            // B: K-major like A, or N-major: 64-column chunks 8192 B apart (LBO),
+            //    8-K-row groups 1024 B apart (SBO); K advance = 16 rows * 128 B
+            const uint64_t db = nmajor_b ? make_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                         : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            tc_mma(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));   // frees the stage when these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(buf));   // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int r = q * 32 + lane;             // row inside the 128-row tile
+    uint32_t acc_it = 0;
+    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++acc_it) {
+      const int e = t / p.tiles_per_matrix;
+      const uint32_t tt = p.tile_tab[t - e * p.tiles_per_matrix];
+      const int i = tt & 0xFF, j = (tt >> 8) & 0xFF, w = (tt >> 16) & 0xFF;
+      const uint32_t buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, ANC_DEV_TIMEOUT_EPI);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const size_t grow = (size_t)e * p.M + (size_t)i * BM + r;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+      for (int cc = 0; cc < 4 * w; ++cc) {
+        uint32_t v[32];
+        tc_ld32(taddr0 + cc * 32, v);
+        tc_wait_ld();
+        const int col = j * 128 + cc * 32;
+        uint16_t *crow = p.C + grow * p.ldc + col;
+        float f[32];
+        if (p.mode == 0) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]);
+        } else {
+          const uint4 *drow = reinterpret_cast<const uint4 *>(p.D + grow * p.ldc + col);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint4 d = drow[k4];
+            const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float dlo = __uint_as_float(dw[k] << 16);
+              const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
+              f[k4 * 8 + 2 * k] =
+                  __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(p.alpha, dlo));
+              f[k4 * 8 + 2 * k + 1] =
+                  __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(p.alpha, dhi));
+            }
+          }
+        }
+        uint32_t h[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) h[k] = pack_bf16(f[2 * k], f[2 * k + 1]);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          reinterpret_cast<uint4 *>(crow)[k4] =
+              make_uint4(h[4 * k4], h[4 * k4 + 1], h[4 * k4 + 2], h[4 * k4 + 3]);
+        if (p.mode != 2) {
+          // mirror: the 128-block (i, hb) with hb < i also lands, transposed, at (hb, i)
+          const int hb = j + (cc >> 2);
+          if (hb < i) {
+            uint16_t *mcol = p.C + ((size_t)e * p.M + (size_t)col) * p.ldc + (size_t)i * BM + r;
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              mcol[(size_t)k * p.ldc] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void *sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || !sym) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  fn = (EncodeTiledFn)sym;
+  return fn;
+}
+
+// 2-D bf16 row-major tensor (rows, cols), box (box_cols=64, box_rows), 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    anc_set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return ANC_E_CUDA;
+  }
+  if (((uintptr_t)ptr & 15) != 0 || (cols * 2) % 16 != 0) {
+    anc_set_error("TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+    return ANC_E_INVALID;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    anc_set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return ANC_E_CUDA;
+  }
+  return ANC_OK;
+}
+
+struct TileTab {
+  uint32_t *d_tab;
+  int count;
+};
+struct GemmCache {
+  std::map<uint64_t, TileTab> tabs;
+  bool attr_set = false;
+};
+std::map<anc_ctx *, GemmCache *> g_caches;
+
+// Tile list of one matrix.  sym: lower-triangular 128-blocks of an (mb x mb) grid packed
+// into 256-wide tiles; else the full (mb x nb) grid.
+int get_tile_tab(anc_ctx *ctx, bool sym, int mb, int nb, TileTab *out) {
+  GemmCache *&gc = g_caches[ctx];
+  if (!gc) gc = new GemmCache();
+  const uint64_t key = ((uint64_t)(sym ? 1 : 0) << 40) | ((uint64_t)mb << 20) | (uint64_t)nb;
+  auto it = gc->tabs.find(key);
+  if (it != gc->tabs.end()) {
+    *out = it->second;
+    return ANC_OK;
+  }
+  std::vector<uint32_t> tab;
+  for (int i = 0; i < mb; ++i) {
+    if (sym) {
+      for (int j = 0; j <= i; j += 2) {
+        const int w = (j + 1 <= i) ? 2 : 1;
+        tab.push_back((uint32_t)i | ((uint32_t)j << 8) | ((uint32_t)w << 16));
+      }
+    } else {
+      for (int j = 0; j < nb; j += 2) {
+        const int w = (nb - j) >= 2 ? 2 : 1;
+        tab.push_back((uint32_t)i | ((uint32_t)j << 8) | ((uint32_t)w << 16));
+      }
+    }
+  }
+  TileTab tt;
+  tt.count = (int)tab.size();
+  ANC_CUDA(cudaMalloc((void **)&tt.d_tab, tab.size() * sizeof(uint32_t)));
+  ANC_CUDA(cudaMemcpy(tt.d_tab, tab.data(), tab.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  gc->tabs[key] = tt;
+  *out = tt;
+  return ANC_OK;
+}
+
+}  // namespace
+
+void anc_gemm_cache_destroy(anc_ctx *ctx) {
+  auto it = g_caches.find(ctx);
+  if (it == g_caches.end()) return;
+  for (auto &kv : it->second->tabs) cudaFree(kv.second.d_tab);
+  delete it->second;
+  g_caches.erase(it);
+}
+
+int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
+                       int E, int M, int N, float alpha, float beta, cudaStream_t st) {
+  ANC_REQUIRE(mode >= 0 && mode <= 2, "bad mode %d", mode);
+  ANC_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0,
+              "Newton-Schulz shape (%d x %d x %d) must be multiples of 128", E, M, N);
+  ANC_REQUIRE(M / 128 <= 255 && N / 128 <= 255, "matrix too large for the tile table");
+  ANC_REQUIRE((size_t)E * M < (1u << 31), "E*M too large");
+  // mode 0: P is (E*M, N), K = N.  modes 1/2: P is (E*M, M), K = M.
+  const int Kdim = mode == 0 ? N : M;
+  const int mb = M / 128;
+  CUtensorMap tmA, tmB;
+  int rc = make_map(&tmA, P, (uint64_t)E * M, (uint64_t)Kdim, 128);
+  if (rc) return rc;
+  if (mode == 2) {
+    ANC_REQUIRE(Q, "mode 2 needs Q");
+    rc = make_map(&tmB, Q, (uint64_t)E * M, (uint64_t)N, 64);
+  } else {
+    rc = make_map(&tmB, P, (uint64_t)E * M, (uint64_t)Kdim, 128);
+  }
+  if (rc) return rc;
+  TileTab tt;
+  rc = get_tile_tab(ctx, mode != 2, mb, mode == 2 ? N / 128 : mb, &tt);
+  if (rc) return rc;
+  GemmCache *gc = g_caches[ctx];
+  if (!gc->attr_set) {
+    ANC_CUDA(cudaFuncSetAttribute(ns_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemBytes));
+    gc->attr_set = true;
+  }
+  GemmParams p;
+  p.D = mode == 0 ? nullptr : (mode == 1 ? P : Q);
+  p.C = C;
+  p.tile_tab = tt.d_tab;
+  p.status = ctx->d_status;
+  p.E = E;
+  p.M = M;
+  p.ldc = mode == 2 ? N : M;
+  p.tiles_per_matrix = tt.count;
+  p.total_tiles = tt.count * E;
+  p.kblocks = Kdim / BK;
+  p.mode = mode;
+  p.alpha = alpha;
+  p.beta = beta;
+  int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
+  ns_gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, p);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+extern "C" int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q,
+                                 uint16_t *C, int E, int M, int N, float alpha, float beta,
+                                 void *stream) {
+  ANC_REQUIRE(ctx && P && C, "NULL argument");
+  anc_device_guard guard(ctx->device);
+  return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, anc_pick_stream(ctx, stream));
+}

@@ -1,0 +1,239 @@
+// Context, device memory, events: the plumbing the reference does with
+// cuda.bindings (cuMemAlloc / cuMemcpy* / cuMemFree in _DBuf, _Buf, _GpuArray).
+#include <string.h>
+#include "anc_internal.h"
+
+static thread_local char g_err[512] = "";
+
+void anc_set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int anc_cuda_fail(cudaError_t e, const char *what) {
+  anc_set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+  return e == cudaErrorMemoryAllocation ? ANC_E_NOMEM : ANC_E_CUDA;
+}
+
+extern "C" {
+
+int anc_version(void) { return 100; }
+
+const char *anc_last_error(void) { return g_err; }
+
+int anc_device_count(int *count) {
+  ANC_REQUIRE(count, "count is NULL");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  *count = n;
+  return ANC_OK;
+}
+
+int anc_ctx_create(int device, void *stream, anc_ctx **out) {
+  ANC_REQUIRE(out, "out is NULL");
+  *out = nullptr;
+  ANC_CUDA(cudaSetDevice(device));
+  ANC_CUDA(cudaFree(0));
+  anc_ctx *c = new anc_ctx();
+  memset(c, 0, sizeof(*c));
+  c->device = device;
+  if (stream) {
+    c->stream = (cudaStream_t)stream;
+    c->own_stream = false;
+  } else {
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+      delete c;
+      return anc_cuda_fail(e, "cudaStreamCreate");
+    }
+    c->own_stream = true;
+  }
+  cudaDeviceProp prop;
+  ANC_CUDA(cudaGetDeviceProperties(&prop, device));
+  c->sm_count = prop.multiProcessorCount;
+  if (prop.major != 10) {
+    anc_set_error("device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major,
+                  prop.minor);
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c;
+    return ANC_E_UNSUPPORTED;
+  }
+  c->work_bytes = 1 << 20;
+  cudaError_t e = cudaMalloc(&c->d_work, c->work_bytes);
+  if (e == cudaSuccess) e = cudaMalloc((void **)&c->d_status, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 256);
+  if (e != cudaSuccess) {
+    delete c;
+    return anc_cuda_fail(e, "ctx workspace");
+  }
+  *out = c;
+  return ANC_OK;
+}
+
+int anc_ctx_destroy(anc_ctx *ctx) {
+  if (!ctx) return ANC_OK;
+  anc_device_guard g(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  anc_gemm_cache_destroy(ctx);
+  if (ctx->d_work) cudaFree(ctx->d_work);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->d_flush) cudaFree(ctx->d_flush);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return ANC_OK;
+}
+
+int anc_ctx_stream(anc_ctx *ctx, void **stream) {
+  ANC_REQUIRE(ctx && stream, "NULL argument");
+  *stream = (void *)ctx->stream;
+  return ANC_OK;
+}
+
+int anc_ctx_sync(anc_ctx *ctx, void *stream) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaStreamSynchronize(anc_pick_stream(ctx, stream)));
+  return ANC_OK;
+}
+
+int anc_ctx_status(anc_ctx *ctx, uint32_t *code) {
+  ANC_REQUIRE(ctx && code, "NULL argument");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaStreamSynchronize(ctx->stream));
+  ANC_CUDA(cudaMemcpy(code, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (*code) ANC_CUDA(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
+  return ANC_OK;
+}
+
+int anc_malloc(anc_ctx *ctx, size_t bytes, void **dptr) {
+  ANC_REQUIRE(ctx && dptr, "NULL argument");
+  anc_device_guard g(ctx->device);
+  *dptr = nullptr;
+  if (bytes == 0) bytes = 256;
+  cudaError_t e = cudaMalloc(dptr, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    anc_set_error("cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    return ANC_E_NOMEM;
+  }
+  return ANC_OK;
+}
+
+int anc_free(anc_ctx *ctx, void *dptr) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  if (!dptr) return ANC_OK;
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaFree(dptr));
+  return ANC_OK;
+}
+
+int anc_memset(anc_ctx *ctx, void *dptr, int byte, size_t bytes, void *stream) {
+  ANC_REQUIRE(ctx && dptr, "NULL argument");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaMemsetAsync(dptr, byte, bytes, anc_pick_stream(ctx, stream)));
+  return ANC_OK;
+}
+
+int anc_h2d(anc_ctx *ctx, void *dptr, const void *hptr, size_t bytes, void *stream, int sync) {
+  ANC_REQUIRE(ctx && dptr && hptr, "NULL argument");
+  anc_device_guard g(ctx->device);
+  cudaStream_t st = anc_pick_stream(ctx, stream);
+  ANC_CUDA(cudaMemcpyAsync(dptr, hptr, bytes, cudaMemcpyHostToDevice, st));
+  if (sync) ANC_CUDA(cudaStreamSynchronize(st));
+  return ANC_OK;
+}
+
+int anc_d2h(anc_ctx *ctx, void *hptr, const void *dptr, size_t bytes, void *stream, int sync) {
+  ANC_REQUIRE(ctx && dptr && hptr, "NULL argument");
+  anc_device_guard g(ctx->device);
+  cudaStream_t st = anc_pick_stream(ctx, stream);
+  ANC_CUDA(cudaMemcpyAsync(hptr, dptr, bytes, cudaMemcpyDeviceToHost, st));
+  if (sync) ANC_CUDA(cudaStreamSynchronize(st));
+  return ANC_OK;
+}
+
+int anc_d2d(anc_ctx *ctx, void *dst, const void *src, size_t bytes, void *stream) {
+  ANC_REQUIRE(ctx && dst && src, "NULL argument");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, anc_pick_stream(ctx, stream)));
+  return ANC_OK;
+}
+
+int anc_host_alloc(size_t bytes, void **hptr) {
+  ANC_REQUIRE(hptr, "hptr is NULL");
+  *hptr = nullptr;
+  cudaError_t e = cudaHostAlloc(hptr, bytes ? bytes : 64, cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    anc_set_error("cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    return ANC_E_NOMEM;
+  }
+  return ANC_OK;
+}
+
+int anc_host_free(void *hptr) {
+  if (hptr) ANC_CUDA(cudaFreeHost(hptr));
+  return ANC_OK;
+}
+
+int anc_event_create(void **ev) {
+  ANC_REQUIRE(ev, "ev is NULL");
+  cudaEvent_t e;
+  ANC_CUDA(cudaEventCreate(&e));
+  *ev = (void *)e;
+  return ANC_OK;
+}
+
+int anc_event_record(void *ev, void *stream) {
+  ANC_REQUIRE(ev, "ev is NULL");
+  ANC_CUDA(cudaEventRecord((cudaEvent_t)ev, (cudaStream_t)stream));
+  return ANC_OK;
+}
+
+int anc_event_sync(void *ev) {
+  ANC_REQUIRE(ev, "ev is NULL");
+  ANC_CUDA(cudaEventSynchronize((cudaEvent_t)ev));
+  return ANC_OK;
+}
+
+int anc_event_elapsed_ms(void *start, void *stop, float *ms) {
+  ANC_REQUIRE(start && stop && ms, "NULL argument");
+  ANC_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+  return ANC_OK;
+}
+
+int anc_event_destroy(void *ev) {
+  if (ev) ANC_CUDA(cudaEventDestroy((cudaEvent_t)ev));
+  return ANC_OK;
+}
+
+__global__ void anc_flush_kernel(uint4 *p, size_t n16) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n16; i += stride) p[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+int anc_flush_l2(anc_ctx *ctx, void *stream) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  anc_device_guard g(ctx->device);
+  if (!ctx->d_flush) {
+    ctx->flush_bytes = (size_t)256 << 20;  // 256 MiB > 126 MB L2
+    cudaError_t e = cudaMalloc(&ctx->d_flush, ctx->flush_bytes);
+    if (e != cudaSuccess) {
+      ctx->d_flush = nullptr;
+      return anc_cuda_fail(e, "flush buffer");
+    }
+  }
+  anc_flush_kernel<<<ctx->sm_count * 8, 256, 0, anc_pick_stream(ctx, stream)>>>(
+      (uint4 *)ctx->d_flush, ctx->flush_bytes / 16);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,233 @@
+/*
+ * ancora_b200.h -- C ABI of libancora_b200.so: the Muon + AdamW hybrid optimizer
+ * step of ancora-cutile (ancora/optim/{adamw,muon,hybrid}.py and
+ * ancora/kernels/muon_ns.py) as hand-written CUDA for sm_100a.
+ *
+ * The reference has no C ABI for this path: its Python classes launch cuda.tile
+ * kernels with ct.launch(stream_int, grid, kernel, args).  Each entry point below
+ * names the reference call site(s) it replaces.  The calling style (opaque handle
+ * from a create call, int status from every call, explicit free) is the one the
+ * reference already uses for its only ctypes plug-in (ancora/model/resident.py:37-47).
+ *
+ * Conventions
+ *   - every function returns 0 on success, a negative ANC_E_* code on failure, and
+ *     never aborts the process; anc_last_error() gives the message for this thread.
+ *   - device pointers are plain void* / typed pointers into CUDA device memory;
+ *     "stream" is a CUstream / cudaStream_t passed as void* (NULL = the context's
+ *     own stream).  The reference passes the same value as a Python int.
+ *   - bf16 values travel as uint16_t bit patterns, as in the reference.
+ *   - calls are asynchronous on the stream unless the name ends in _sync or the
+ *     comment says otherwise (reference: ResidentLayerTrain.step is async,
+ *     ancora/model/resident_train.py:336-339).
+ */
+#ifndef ANCORA_B200_H_
+#define ANCORA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ANC_API __attribute__((visibility("default")))
+
+/* status codes */
+#define ANC_OK 0
+#define ANC_E_INVALID (-1)    /* bad argument (shape, alignment, null pointer)          */
+#define ANC_E_CUDA (-2)       /* a CUDA runtime / driver call failed                    */
+#define ANC_E_NOMEM (-3)      /* device or host allocation failed                       */
+#define ANC_E_DEVICE (-4)     /* a kernel reported a bounded-wait timeout / bad index   */
+#define ANC_E_NCCL (-5)       /* NCCL missing or a collective failed                    */
+#define ANC_E_UNSUPPORTED (-6)
+
+/* gradient element type */
+#define ANC_GRAD_BF16 0
+#define ANC_GRAD_F32 1
+
+/* bf16 rounding of the parameter copy */
+#define ANC_ROUND_RNE 0 /* ancora/optim/adamw.py:41 */
+#define ANC_ROUND_SR 1  /* Philox4x32-10 dither, bit rule of ancora/kernels/fused.py:159-161 */
+
+typedef struct anc_ctx anc_ctx;
+typedef struct anc_adamw_plan anc_adamw_plan;
+typedef struct anc_muon_plan anc_muon_plan;
+typedef struct anc_comm anc_comm;
+
+/* ---------------------------------------------------------------- runtime ---- */
+
+ANC_API int anc_version(void);
+ANC_API const char *anc_last_error(void);
+ANC_API int anc_device_count(int *count);
+
+/* Context = (device, stream, small device workspace, device status word).
+ * Replaces the reference's per-script bootstrap (cudart.cudaFree(0); Device(0);
+ * create_stream(): tests/optim/test_adamw.py:15-17).  stream==NULL creates one. */
+ANC_API int anc_ctx_create(int device, void *stream, anc_ctx **out);
+ANC_API int anc_ctx_destroy(anc_ctx *ctx);
+ANC_API int anc_ctx_stream(anc_ctx *ctx, void **stream);
+ANC_API int anc_ctx_sync(anc_ctx *ctx, void *stream);
+/* Reads and clears the device status word (0 = no kernel reported a problem). */
+ANC_API int anc_ctx_status(anc_ctx *ctx, uint32_t *code);
+
+/* Device buffers: replace cuMemAlloc / cuMemcpyHtoD / cuMemcpyDtoH / cuMemFree in
+ * _DBuf (ancora/model/resident.py:52-94), _Buf (ancora/optim/adamw.py:51-60) and
+ * _GpuArray (ancora/kernels/loss.py:277-294). */
+ANC_API int anc_malloc(anc_ctx *ctx, size_t bytes, void **dptr);
+ANC_API int anc_free(anc_ctx *ctx, void *dptr);
+ANC_API int anc_memset(anc_ctx *ctx, void *dptr, int byte, size_t bytes, void *stream);
+ANC_API int anc_h2d(anc_ctx *ctx, void *dptr, const void *hptr, size_t bytes, void *stream, int sync);
+ANC_API int anc_d2h(anc_ctx *ctx, void *hptr, const void *dptr, size_t bytes, void *stream, int sync);
+ANC_API int anc_d2d(anc_ctx *ctx, void *dst, const void *src, size_t bytes, void *stream);
+ANC_API int anc_host_alloc(size_t bytes, void **hptr); /* pinned */
+ANC_API int anc_host_free(void *hptr);
+
+/* CUDA events on the caller's stream (timing in the benchmark). */
+ANC_API int anc_event_create(void **ev);
+ANC_API int anc_event_record(void *ev, void *stream);
+ANC_API int anc_event_sync(void *ev);
+ANC_API int anc_event_elapsed_ms(void *start, void *stop, float *ms);
+ANC_API int anc_event_destroy(void *ev);
+
+/* Writes `bytes` of device memory (larger than L2) to evict cached lines between
+ * timed iterations. */
+ANC_API int anc_flush_l2(anc_ctx *ctx, void *stream);
+
+/* ------------------------------------------------------------------ AdamW ---- */
+
+/* One tensor of the multi-tensor AdamW arena.  elem_offset is the index of the
+ * tensor's first element in the global (un-sharded) arena and must be a multiple
+ * of 8: it keys the stochastic-rounding stream, so results do not depend on how the
+ * arena is sharded or launched. */
+typedef struct anc_adamw_tensor {
+  const void *g; /* gradient, bf16 bits or f32 (plan's grad_dtype)            */
+  float *p32;    /* fp32 master, updated in place                              */
+  float *m;      /* first moment                                               */
+  float *v;      /* second moment                                              */
+  uint16_t *p16; /* bf16 parameter copy the forward reads, written every step  */
+  uint64_t numel;
+  uint64_t elem_offset;
+  float wd; /* decoupled weight decay for this tensor (0 for no_decay names) */
+  float _pad;
+} anc_adamw_tensor;
+
+/* Scalars of one step, already float32 (the host materialises 1-beta and the bias
+ * corrections once so that the kernel and the CPU oracle use identical values). */
+typedef struct anc_adamw_scalars {
+  float beta1, one_minus_beta1, beta2, one_minus_beta2, eps, lr, ibc1, ibc2;
+} anc_adamw_scalars;
+
+/* Builds the device tensor table + chunk table.  Replaces the per-tensor state dict
+ * built in AdamW.__init__ (ancora/optim/adamw.py:74-86) and the per-tensor launch
+ * loop in AdamW.step (adamw.py:92-97) / ResidentLayerTrain.step
+ * (ancora/model/resident_train.py:349-353): one launch covers all tensors. */
+ANC_API int anc_adamw_plan_create(anc_ctx *ctx, const anc_adamw_tensor *tensors, int n_tensors,
+                                  int grad_dtype, anc_adamw_plan **out);
+/* Restricts the plan to the arena slice [begin, end) (ZeRO-1 ownership; both
+ * multiples of 8).  begin=0,end=UINT64_MAX restores the whole arena. */
+ANC_API int anc_adamw_plan_set_range(anc_adamw_plan *plan, uint64_t begin, uint64_t end);
+ANC_API int anc_adamw_plan_total(anc_adamw_plan *plan, uint64_t *arena_elems, uint64_t *owned_elems);
+/* The fused step: replaces ct.launch(si, (R//otm,1,1), _adamw, ...) of
+ * ancora/optim/adamw.py:23-41.  seed/step key the Philox stream (ANC_ROUND_SR). */
+ANC_API int anc_adamw_step(anc_adamw_plan *plan, const anc_adamw_scalars *s, int rounding,
+                           uint64_t seed, uint64_t step, void *stream);
+ANC_API int anc_adamw_plan_destroy(anc_adamw_plan *plan);
+
+/* ------------------------------------------------------------------- Muon ---- */
+
+/* One 2-D weight under Muon.  (K,N) is the stored orientation; Newton-Schulz runs
+ * on the orientation with rows <= cols (ancora/optim/muon.py:72-74,99-100). */
+typedef struct anc_muon_weight {
+  float *buf;    /* momentum, f32 (K,N), the only persistent Muon state          */
+  const void *g; /* gradient (K,N), bf16 bits or f32                             */
+  float *p32;    /* fp32 master (K,N), updated in place                          */
+  uint16_t *p16; /* bf16 weight (K,N) the forward reads, refreshed every step    */
+  int32_t K, N;
+  int32_t owner; /* ZeRO-1 owner rank of this matrix; -1 = always mine           */
+  int32_t _pad;
+} anc_muon_weight;
+
+/* Groups weights by Newton-Schulz shape (min(K,N), max(K,N)), allocates the packed
+ * bf16 scratch (X, Y, A, B per group, shared across groups) and encodes the TMA
+ * tensor maps.  Replaces BatchedProjMuon.__init__ / MuonScratch / ExpertMuonScratch
+ * (ancora/optim/muon.py:137-161,223-254; ancora/kernels/moe.py:404-421).
+ * K and N must be multiples of 128 (reference: muon.py:98,172,233).
+ * my_rank selects which weights this plan steps (owner == my_rank or owner < 0);
+ * max_batch <= 0 batches a whole shape group at once. */
+ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_weights,
+                                 int grad_dtype, int my_rank, int max_batch, anc_muon_plan **out);
+/* One Muon step for every owned weight: momentum + Nesterov -> packed bf16 u
+ * (transposed for tall weights) -> Frobenius normalisation -> ns_steps Newton-Schulz
+ * iterations with coeffs[k] = (a,b,c) -> master update + bf16 refresh.  Replaces
+ * BatchedProjMuon.step (ancora/optim/muon.py:256-277), ResidentMuon.step
+ * (muon.py:180-201) and the expert branch of GroupedMoEFFN.step
+ * (ancora/kernels/moe.py:578-588).  coeffs holds 3*ns_steps floats.  lr is a double
+ * because the reference forms lr*sqrt(max(1,K/N)) in double before the single float32
+ * rounding (muon.py:176,200). */
+ANC_API int anc_muon_step(anc_muon_plan *plan, double lr, float momentum, int nesterov, int ns_steps,
+                          const float *coeffs, float eps, void *stream);
+/* Per-phase device time of the most recent anc_muon_step when timing was enabled
+ * with anc_muon_plan_set_timing(plan, 1): ms spent in momentum, normalise,
+ * Newton-Schulz GEMMs and update; and the algorithmic FLOPs of those GEMMs. */
+ANC_API int anc_muon_plan_set_timing(anc_muon_plan *plan, int on);
+ANC_API int anc_muon_plan_last_timing(anc_muon_plan *plan, float ms[4], double *ns_flops,
+                                      int *ns_launches);
+ANC_API int anc_muon_plan_scratch_bytes(anc_muon_plan *plan, uint64_t *bytes);
+ANC_API int anc_muon_plan_destroy(anc_muon_plan *plan);
+
+/* Bare batched Newton-Schulz on caller-owned packed buffers: replaces
+ * newton_schulz_resident / newton_schulz_resident_e
+ * (ancora/kernels/muon_ns.py:245-283,430-468).  X (E*M,N) bf16 bits is overwritten
+ * with the result; A,B (E*M,M) and Y (E*M,N) are bf16 scratch; recip (E) f32.
+ * M <= N, both multiples of 128.  All buffers 1024-byte aligned. */
+ANC_API int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y,
+                           float *recip, int E, int M, int N, int steps, const float *coeffs,
+                           float eps, void *stream);
+
+/* One batched GEMM phase of the chain, exposed for kernel-level parity tests
+ * (reference kernels: _e_gemm_nt_tril + _e_mirror, _e_gemm_axpy_tril + _e_mirror,
+ * _e_gemm_axpy: ancora/kernels/muon_ns.py:331-384).
+ *   mode 0: C = RNE(P P^T)                      P (E*M,K)  -> C (E*M,M), symmetric
+ *   mode 1: C = RNE(alpha*P + beta*(P P^T))     P (E*M,M) symmetric -> C (E*M,M)
+ *   mode 2: C = RNE(alpha*Q + beta*(P Q))       P (E*M,M), Q (E*M,N) -> C (E*M,N) */
+ANC_API int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q,
+                              uint16_t *C, int E, int M, int N, float alpha, float beta,
+                              void *stream);
+
+/* Muon elementwise kernels on their own (kernel-level parity tests; reference:
+ * _muon_mom/_muon_mom_t and _muon_update_cast/_muon_update_cast_t,
+ * ancora/kernels/muon_ns.py:177-242).  `transposed` selects the tall-weight forms
+ * whose packed operand is (N,K). */
+ANC_API int anc_muon_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u,
+                              int K, int N, float momentum, int nesterov, int transposed,
+                              void *stream);
+ANC_API int anc_muon_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O, int K, int N,
+                            float lr_scale, int transposed, void *stream);
+/* recip[e] = 1/(||X_e||_F + eps) by a fixed-order two-level reduction, then
+ * X_e = RNE(X_e * recip[e]) in place (reference: _e_fro_recip + _e_scale,
+ * ancora/kernels/muon_ns.py:387-406). */
+ANC_API int anc_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
+                              void *stream);
+
+/* ----------------------------------------------------------------- ZeRO-1 ---- */
+/* No counterpart in the reference (single GPU, ancora README.md:93).  NCCL is
+ * opened with dlopen at first use; nccl_path may be NULL (default search). */
+#define ANC_NCCL_UNIQUE_ID_BYTES 128
+ANC_API int anc_nccl_load(const char *nccl_path);
+ANC_API int anc_nccl_unique_id(void *id128);
+ANC_API int anc_comm_create(anc_ctx *ctx, const void *id128, int rank, int world, anc_comm **out);
+ANC_API int anc_comm_destroy(anc_comm *comm);
+/* In-place all-gather of equal contiguous slices: rank r owns
+ * [r*elems_per_rank, (r+1)*elems_per_rank) of `arena` (bf16 elements). */
+ANC_API int anc_comm_allgather_bf16(anc_comm *comm, uint16_t *arena, uint64_t elems_per_rank,
+                                    void *stream);
+/* Grouped broadcasts of variable segments: segment i (ptr[i], elems[i]) is sent
+ * by root[i] to everybody. */
+ANC_API int anc_comm_bcast_segments(anc_comm *comm, uint16_t *const *ptr, const uint64_t *elems,
+                                    const int *root, int n_segments, void *stream);
+ANC_API int anc_comm_barrier(anc_comm *comm, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANCORA_B200_H_ */

@@ -1,0 +1,111 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE's own
+Python code (ancora-cutile checked out at the path given on the command line).
+
+    python tests/golden/make_golden.py /path/to/ancora-cutile
+
+The reference imports ``cuda.core`` at module scope (ancora/kernels/loss.py:30) but
+uses nothing from it at import time, so an empty stand-in module is registered
+before importing.  Only host (numpy) code of the reference is executed:
+
+* ancora.optim.muon.newton_schulz5            -> ns_keller.npz
+* tests/kernels/_probe_polar_express.ns + PE  -> ns_pe.npz
+* ancora.optim.muon.Muon (3 steps)            -> host_muon.npz
+* ancora.optim.adamw._bf16_bits/_bits_f32,
+  ancora.optim.muon._bf                       -> bf16.npz
+* ancora.kernels.muon_ns.PE_SCHEDULE/_coef_at,
+  ancora.optim.hybrid.default_is_muon         -> tables.json
+
+The reference's AdamW runs only on a GPU (cuda.tile kernel); it has no host
+function to call, so AdamW has no file here: its oracle is pinned by the formula
+the reference's own test states (tests/optim/test_adamw.py:37-41) at that test's
+tolerance, in tests/test_oracle_golden.py.
+"""
+import importlib.util
+import json
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main(ref_root):
+    sys.path.insert(0, ref_root)
+    sys.modules.setdefault("cuda.core", types.ModuleType("cuda.core"))
+    from ancora.optim.muon import newton_schulz5, Muon, _bf
+    from ancora.optim.adamw import _bf16_bits, _bits_f32
+    from ancora.optim.hybrid import default_is_muon
+    from ancora.kernels.muon_ns import PE_SCHEDULE, _coef_at, A_COEF, B_COEF, C_COEF
+
+    spec = importlib.util.spec_from_file_location(
+        "_probe_pe", os.path.join(ref_root, "tests", "kernels", "_probe_polar_express.py"))
+    probe = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(probe)
+
+    rng = np.random.default_rng(20240607)
+
+    # 1. Keller fp32 Newton-Schulz, wide / tall / square
+    out = {}
+    for i, shp in enumerate([(128, 256), (256, 128), (128, 128)]):
+        G = (rng.standard_normal(shp) * 1e-3).astype(np.float32)
+        out[f"in{i}"] = G
+        out[f"out{i}"] = newton_schulz5(G, 5)
+    np.savez_compressed(os.path.join(HERE, "ns_keller.npz"), **out)
+
+    # 2. Polar-Express fp32 Newton-Schulz (host probe's ns())
+    out = {}
+    for i, shp in enumerate([(128, 256), (128, 128)]):
+        X = (rng.standard_normal(shp) @ np.diag(rng.uniform(0.1, 3.0, shp[1]))).astype(np.float32)
+        out[f"in{i}"] = X
+        out[f"out{i}"] = probe.ns(X, probe.PE, 5).astype(np.float32)
+        out[f"out{i}_n7"] = probe.ns(X, probe.PE, 7).astype(np.float32)   # tail triple repeats
+    np.savez_compressed(os.path.join(HERE, "ns_pe.npz"), **out)
+
+    # 3. host Muon, 3 steps, one tall and one wide weight
+    P = {"tall": (rng.standard_normal((256, 128)) * 0.02).astype(np.float32),
+         "wide": (rng.standard_normal((128, 256)) * 0.02).astype(np.float32)}
+    opt = Muon(P, lr=0.02, momentum=0.95, nesterov=True, ns_steps=5)
+    out = {f"p_{k}": v for k, v in P.items()}
+    for t in range(3):
+        g = {k: (rng.standard_normal(v.shape) * 1e-3).astype(np.float32) for k, v in P.items()}
+        for k, v in g.items():
+            out[f"g{t}_{k}"] = v
+        opt.step(g)
+    for k in P:
+        out[f"master_{k}"] = opt.master()[k]
+        out[f"weights_{k}"] = opt.weights()[k]
+        out[f"buf_{k}"] = opt.buf[k]
+    np.savez_compressed(os.path.join(HERE, "host_muon.npz"), **out)
+
+    # 4. bf16 rounding helpers (ties, subnormals, infinities, signed zeros, random)
+    edge = np.array([0.0, -0.0, 1.0, -1.0, 1.00390625, 1.01171875, 1.0078125, 3.0e38, -3.0e38,
+                     3.3895314e38, np.inf, -np.inf, 1e-40, -1e-40, 1.17549435e-38, 65504.0],
+                    dtype=np.float32)
+    ties = (np.arange(0x3F800000, 0x3F800000 + 8 * 0x8000, 0x8000, dtype=np.uint32)).view(np.float32)
+    x = np.concatenate([edge, ties, (rng.standard_normal(4096) * 0.02).astype(np.float32)])
+    bits = _bf16_bits(x)
+    np.savez_compressed(os.path.join(HERE, "bf16.npz"), x=x, bits=bits, back=_bits_f32(bits), bf=_bf(x))
+
+    # 5. tables
+    names = (["embed", "final_norm", "lm_head"] +
+             [f"layers.{l}.{n}" for l in range(2) for n in
+              ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj",
+               "input_ln", "post_ln", "q_norm", "k_norm", "router", "experts.3.gate_proj")])
+    two_d = lambda n: not any(t in n for t in ("_ln", "norm"))
+    routing = {n: bool(default_is_muon(n, np.zeros((2, 2) if two_d(n) else (2,)))) for n in names}
+    tables = {
+        "keller": [A_COEF, B_COEF, C_COEF],
+        "pe_schedule": [list(t) for t in PE_SCHEDULE],
+        "coef_at_pe": [list(_coef_at(PE_SCHEDULE, k)) for k in range(8)],
+        "coef_at_none": [list(_coef_at(None, k)) for k in range(3)],
+        "routing": routing,
+    }
+    with open(os.path.join(HERE, "tables.json"), "w") as f:
+        json.dump(tables, f, indent=1, sort_keys=True)
+    print("wrote fixtures to", HERE)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
