@@ -9,8 +9,10 @@ from .muon import BatchedProjMuon, Muon, MuonPlan, MuonScratch, ResidentMuon
 from .muon_ns import (PE_SCHEDULE, newton_schulz_resident, newton_schulz_resident_e,
                       set_polar_express)
 from .hybrid import HybridOptimizer, default_is_muon
+from .resident import ResidentHybrid
 
 __all__ = ["AncoraError", "LIB_PATH", "Context", "DBuf", "Event", "PinnedArray", "dev_ptr",
            "get_context", "set_device", "AdamW", "ResidentAdamW", "BatchedProjMuon", "Muon",
            "MuonPlan", "MuonScratch", "ResidentMuon", "PE_SCHEDULE", "newton_schulz_resident",
-           "newton_schulz_resident_e", "set_polar_express", "HybridOptimizer", "default_is_muon"]
+           "newton_schulz_resident_e", "set_polar_express", "HybridOptimizer", "default_is_muon",
+           "ResidentHybrid"]

@@ -163,13 +163,6 @@ int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, in
   anc_ctx *ctx = pl->ctx;
   anc_device_guard guard(ctx->device);
   cudaStream_t st = anc_pick_stream(ctx, stream);
-  for (auto &s : pl->spans) {
-    cudaEventDestroy(s.a);
-    cudaEventDestroy(s.b);
-  }
-  pl->spans.clear();
-  pl->last_flops = 0.0;
-  pl->last_launches = 0;
   auto begin_span = [&](int phase) {
     if (!pl->timing) return;
     TimedSpan sp;
@@ -236,6 +229,13 @@ int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double *ns_flops, 
   }
   if (ns_flops) *ns_flops = pl->last_flops;
   if (ns_launches) *ns_launches = pl->last_launches;
+  for (auto &s : pl->spans) {
+    cudaEventDestroy(s.a);
+    cudaEventDestroy(s.b);
+  }
+  pl->spans.clear();
+  pl->last_flops = 0.0;
+  pl->last_launches = 0;
   return ANC_OK;
 }
 

@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the hybrid Muon + AdamW optimizer step on Qwen3-0.6B shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload qwen3|moe]
+
+One "step" = one full optimizer step over all 596 M parameters (196 Muon matrices, the tied
+embedding and 113 gain vectors under AdamW), synthetic seeded state, bf16 gradients,
+Polar-Express Newton-Schulz (5 iterations), stochastic-rounded bf16 AdamW output.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) the step is ZeRO-1 sharded
+and ends with the NCCL all-gather of the updated bf16 parameters.
+
+Prints ONE JSON line on rank 0.  `value` is parameters updated per second over the whole job
+with all inputs resident in HBM; `e2e` is the same through HybridOptimizer.step with host
+gradients (page-locked) copied in and the updated bf16 weights copied out inside the timed
+region.  `--impl reference` times the reference's numpy formulation (the CPU oracle port) on
+the host cores over a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ADAMW_KW = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, wd=0.1)
+MUON_KW = dict(lr=0.02, momentum=0.95, nesterov=True, ns_steps=5)
+SEED_SR = 1234
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), src="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake"}
+
+    def __init__(self, device):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(device)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.th = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def start(self):
+        if self.nv:
+            self.th.start()
+
+    def stop(self):
+        self._stop.set()
+        if self.nv and self.th.is_alive():
+            self.th.join(1.0)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def workload_shapes(name):
+    from ancora_cutile_b200 import shapes
+    if name == "qwen3":
+        return shapes.qwen3_0_6b_shapes(), "qwen3-0.6b hybrid optimizer step (28 layers, d=1024, ffn=3072, vocab=151936)"
+    return shapes.moe_family_shapes(), "moe-family hybrid optimizer step (24 layers, 16x(768x1024) experts per MoE layer)"
+
+
+def route(shp):
+    from ancora_cutile_b200.hybrid import default_is_muon
+    return [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_sample_step(shp, muon_names, layers=1, adamw_elems=1 << 24):
+    """Builds a bounded sample of the workload for the numpy port: the Muon matrices of the
+    first `layers` layers and `adamw_elems` elements of the embedding.  Returns a callable
+    running one step on it plus the scale factors to the full workload."""
+    from oracle import adamw_ref, muon_ref
+    rng = np.random.default_rng(0)
+    sel = [n for n in muon_names if int(n.split(".")[1]) < layers]
+    P = {n: (rng.standard_normal(shp[n], dtype=np.float32) * np.float32(0.02)) for n in sel}
+    G = {n: (rng.standard_normal(shp[n], dtype=np.float32) * np.float32(1e-3)) for n in sel}
+    opt = muon_ref.HostMuon(P, lr=MUON_KW["lr"], momentum=MUON_KW["momentum"], nesterov=True,
+                            ns_steps=MUON_KW["ns_steps"], schedule=muon_ref.PE_SCHEDULE)
+    n = adamw_elems
+    p = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)
+    m = rng.standard_normal(n, dtype=np.float32) * np.float32(1e-4)
+    v = np.abs(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-6))
+    g = rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3)
+    st = {"p": p, "m": m, "v": v, "t": 0}
+
+    def step():
+        t0 = time.perf_counter()
+        opt.step(G)
+        t1 = time.perf_counter()
+        st["t"] += 1
+        s = adamw_ref.adamw_scalars(ADAMW_KW["lr"], *ADAMW_KW["betas"], ADAMW_KW["eps"], st["t"])
+        st["p"], st["m"], st["v"], _ = adamw_ref.adamw_step(st["p"], st["m"], st["v"], g, s, ADAMW_KW["wd"],
+                                                           "sr", SEED_SR, st["t"], 0)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+    from ancora_cutile_b200.zero1 import ns_cost
+    muon_scale = sum(ns_cost(*shp[k]) for k in muon_names) / max(sum(ns_cost(*shp[k]) for k in sel), 1)
+    a_total = sum(int(np.prod(s)) for k, s in shp.items() if k not in set(muon_names))
+    return step, muon_scale, a_total / n, len(sel), n
+
+
+def run_cpu(shp, muon_names, total_params, steps, warmup):
+    step, ms, as_, nsel, n = cpu_sample_step(shp, muon_names)
+    for _ in range(warmup):
+        step()
+    tm = ta = 0.0
+    for _ in range(steps):
+        a, b = step()
+        tm += a
+        ta += b
+    full_s = (tm * ms + ta * as_) / steps
+    cores = os.cpu_count() or 1
+    sample = (f"numpy port of the reference host step: Muon (fp32 Newton-Schulz, BLAS) on the {nsel} "
+              f"matrices of 1 layer scaled x{ms:.1f} by NS cost, AdamW+SR on {n} embedding elements "
+              f"scaled x{as_:.2f}; {steps} step(s), numpy {np.__version__}")
+    return total_params / full_s, full_s * 1e3, cores, sample
+
+
+# ------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen3", choices=["qwen3", "moe"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    shp, wl_name = workload_shapes(args.workload)
+    muon_names = route(shp)
+    total_params = int(sum(int(np.prod(s)) for s in shp.values()))
+    config = {"workload": wl_name, "params": total_params, "muon_matrices": len(muon_names),
+              "grad_dtype": "bf16", "ns": "polar-express x5", "adamw_rounding": "philox-sr",
+              "parallelism": f"zero1x{world}" if world > 1 else "single",
+              "l2": "state (7 GB) is far larger than L2; no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        v, ms, cores, sample = run_cpu(shp, muon_names, total_params, max(args.steps, 1), min(args.warmup, 1))
+        print(json.dumps({
+            "impl": "reference", "metric": "hybrid_optimizer_step_params_per_s", "value": v, "unit": "params/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": v, "unit": "params/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import ancora_cutile_b200 as anc
+    from ancora_cutile_b200 import shapes as S
+    from ancora_cutile_b200.zero1 import Comm, nccl_unique_id
+
+    anc.set_device(local_rank)
+    ctx = anc.get_context()
+    comm = None
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        box = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = Comm(ctx, box[0], rank, world)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    anc.set_polar_express(True)
+    params = S.synthetic_params(shp, seed=0)
+    no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
+    eng = anc.ResidentHybrid(params, muon_names, no_decay_names=no_decay, adamw_kw=ADAMW_KW, muon_kw=MUON_KW,
+                             grad_dtype="bf16", rounding="sr", seed=SEED_SR, rank=rank, world=world,
+                             comm=comm, ctx=ctx)
+    del params
+    # synthetic bf16 gradients, written into the page-locked staging views and uploaded once
+    pin = eng.pinned_grads()
+    S.synthetic_grads_bf16(shp, seed=1, out=pin)
+    eng.upload_grads(pin, ctx.stream)
+    # optimizer state as BASELINE configs describe: m ~ N(0,1e-4), v = |N(0,1e-6)|, momentum ~ N(0,1e-3)
+    rng = np.random.default_rng(2 + rank)
+    for buf, std, absval in ((eng.a_m, 1e-4, False), (eng.a_v, 1e-6, True), (eng.m_buf, 1e-3, False)):
+        n = buf.shape[0]
+        blk = rng.standard_normal(min(n, 1 << 24), dtype=np.float32) * np.float32(std)
+        if absval:
+            blk = np.abs(blk)
+        for o in range(0, n, blk.size):
+            k = min(blk.size, n - o)
+            buf.slice_elems(o, k).upload(blk[:k])
+    ctx.sync()
+
+    if eng.muon is not None:
+        eng.muon.set_timing(True)
+    e0, e1 = anc.Event(), anc.Event()
+    ea = [(anc.Event(), anc.Event()) for _ in range(args.steps)]
+
+    for _ in range(args.warmup):
+        eng.step(ctx.stream)
+    barrier()
+    if eng.muon is not None:
+        eng.muon.last_timing()          # drop the warm-up spans
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ns_ms = mom_ms = upd_ms = nrm_ms = adamw_ms = 0.0
+    ns_flops = 0.0
+    gemm_launches = 0
+    barrier()
+    e0.record(ctx.stream)
+    for k in range(args.steps):
+        # the step, with the AdamW launch bracketed by events (events do not synchronise)
+        ea0, ea1 = ea[k]
+        eng.t += 1
+        a, m = eng.adamw_kw, eng.muon_kw
+        if eng.muon is not None:
+            eng.muon.step(ctx.stream, m["lr"], m["momentum"], m["nesterov"], m["ns_steps"], anc.PE_SCHEDULE)
+        ea0.record(ctx.stream)
+        eng.adamw.step(ctx.stream, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=eng.t)
+        ea1.record(ctx.stream)
+        if world > 1:
+            eng.exchange(ctx.stream)
+    e1.record(ctx.stream)
+    barrier()
+    adamw_ms = sum(a0.elapsed_ms(a1) for a0, a1 in ea)
+    if eng.muon is not None:
+        t = eng.muon.last_timing()      # per-phase spans accumulated over the K timed steps
+        ns_ms, mom_ms, upd_ms, nrm_ms = t["ns_ms"], t["momentum_ms"], t["update_ms"], t["normalize_ms"]
+        ns_flops, gemm_launches = t["ns_flops"], t["ns_launches"]
+    clocks = sampler.stop()
+    total_ms = max_over_ranks(e0.elapsed_ms(e1))
+    ms_per_step = total_ms / args.steps
+    value = total_params / (ms_per_step * 1e-3)
+    K = args.steps
+    peaks = measured_peaks()
+    ns_tflops = ns_flops / (ns_ms * 1e-3) / 1e12 if ns_ms > 0 else 0.0
+    a_owned = min(eng.a_total, eng.a_end) - min(eng.a_total, eng.a_begin)
+    adamw_gbs = 28.0 * a_owned / (adamw_ms / K * 1e-3) / 1e9 if adamw_ms > 0 else 0.0
+    m_owned = eng.m_p32.shape[0] if eng.muon is not None else 0
+    elem_gbs = 24.0 * m_owned / ((mom_ms + upd_ms) / K * 1e-3) / 1e9 if (mom_ms + upd_ms) > 0 else 0.0
+    n_groups = len({(min(shp[n]), max(shp[n])) for n in muon_names})
+    out = {
+        "metric": "hybrid_optimizer_step_params_per_s", "value": value, "unit": "params/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": config,
+        "roofline": {"bound": "tensor", "kernel": "ns_gemm_kernel", "achieved": ns_tflops,
+                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": ns_tflops / peaks["bf16_tflops_sustained"], "traffic": None,
+                     "peak_kind": f"{peaks['src']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
+                     "frac_of_burst": ns_tflops / peaks["bf16_tflops"],
+                     "flops_per_step": ns_flops / K, "ms_per_step": ns_ms / K, "launches_per_step": gemm_launches // K},
+        "adamw": {"bound": "hbm", "achieved": adamw_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                  "frac": adamw_gbs / peaks["hbm_gbs"], "frac_of_8tbs_nominal": adamw_gbs / 8000.0,
+                  "bytes_per_param": 28, "params": a_owned, "ms_per_step": adamw_ms / K},
+        "muon_elementwise": {"bound": "hbm", "achieved": elem_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": elem_gbs / peaks["hbm_gbs"], "bytes_per_param": 24,
+                             "momentum_ms": mom_ms / K, "update_ms": upd_ms / K, "normalize_ms": nrm_ms / K},
+        "clocks": clocks,
+        "gpu_launches": (gemm_launches // K) + 4 * n_groups + 1,
+        "state_bytes_per_gpu": eng.state_bytes() + (eng.muon.scratch_bytes() if eng.muon else 0),
+    }
+
+    # ---- end-to-end: host gradients in, bf16 weights out, through the public class ----
+    if not args.no_e2e:
+        h2d = d2h = 0
+        for _ in range(2):
+            eng.upload_grads(pin, ctx.stream); eng.step(ctx.stream); eng.download_weights_bits(ctx.stream)
+        barrier()
+        e0.record(ctx.stream)
+        for _ in range(args.steps):
+            h2d = eng.upload_grads(pin, ctx.stream)
+            eng.step(ctx.stream)
+            _, d2h = eng.download_weights_bits(ctx.stream, sync=True)
+        e1.record(ctx.stream)
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_ms(e1)) / args.steps
+        out["e2e"] = {"value": total_params / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                      "api": "ResidentHybrid.upload_grads + step + download_weights_bits (the calls HybridOptimizer.step/weights make)"}
+    status = ctx.status()
+    out["device_status"] = status
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, ms, cores, sample = run_cpu(shp, muon_names, total_params, 1, 0)
+        out["cpu_baseline"] = {"value": v, "unit": "params/s", "ms_per_step": ms, "cores": cores,
+                               "kind": "port", "sample": sample}
+    if rank == 0:
+        print(json.dumps(out))
+    eng.free()
+    if comm is not None:
+        comm.destroy()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

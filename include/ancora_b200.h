@@ -166,9 +166,11 @@ ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, i
  * rounding (muon.py:176,200). */
 ANC_API int anc_muon_step(anc_muon_plan *plan, double lr, float momentum, int nesterov, int ns_steps,
                           const float *coeffs, float eps, void *stream);
-/* Per-phase device time of the most recent anc_muon_step when timing was enabled
- * with anc_muon_plan_set_timing(plan, 1): ms spent in momentum, normalise,
- * Newton-Schulz GEMMs and update; and the algorithmic FLOPs of those GEMMs. */
+/* Per-phase device time accumulated over every anc_muon_step since the previous call
+ * (timing enabled with anc_muon_plan_set_timing(plan, 1); CUDA events on the step's
+ * stream, no synchronisation inside the step): ms spent in momentum, normalise,
+ * Newton-Schulz GEMMs and update; the algorithmic FLOPs and the launch count of those
+ * GEMMs.  The call waits for the recorded events, then resets the accumulators. */
 ANC_API int anc_muon_plan_set_timing(anc_muon_plan *plan, int on);
 ANC_API int anc_muon_plan_last_timing(anc_muon_plan *plan, float ms[4], double *ns_flops,
                                       int *ns_launches);

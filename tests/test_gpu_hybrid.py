@@ -1,0 +1,103 @@
+"""GPU: the hybrid optimizer end to end on a small model, and ZeRO-1 sharding.
+
+ZeRO-1 is checked on ONE GPU by building the rank-r engine of a world of 2 and of 4 one
+after another (no collective): the bf16 parameters each rank owns and its fp32 state must
+equal the single-GPU engine's bit for bit."""
+import numpy as np
+import pytest
+
+import ancora_cutile_b200 as anc
+from ancora_cutile_b200 import shapes as S
+from ancora_cutile_b200.bf16 import f32_to_bf16_bits
+from oracle import adamw_ref, bf16 as obf, muon_ref
+
+pytestmark = pytest.mark.gpu
+AKW = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, wd=0.1)
+
+
+def small_shapes():
+    return S.qwen3_0_6b_shapes(n_layers=2, hidden=128, q_heads=2, kv_heads=1, head_dim=128, ffn=384, vocab=1000)
+
+
+def test_routing_matches_reference_rule():
+    shp = S.qwen3_0_6b_shapes()
+    params = {n: np.empty((0,) * len(s)) for n, s in shp.items()}
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    assert len(mu) == 196 and len(shp) - len(mu) == 114
+    assert sum(int(np.prod(shp[n])) for n in shp if n not in mu) == 155_648_000
+
+
+def test_hybrid_step_vs_oracle(ctx):
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=0)
+    rng = np.random.default_rng(1)
+    prev = anc.set_polar_express(True)
+    try:
+        opt = anc.HybridOptimizer(params, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=1234, ctx=ctx)
+        r = opt.routing()
+        assert len(r["muon"]) == 14 and "embed" in r["adamw"]
+        ref_mu = muon_ref.HostMuon({n: params[n] for n in r["muon"]}, schedule=muon_ref.PE_SCHEDULE)
+        st = {n: [params[n].reshape(-1).copy(), np.zeros(params[n].size, np.float32), np.zeros(params[n].size, np.float32)]
+              for n in r["adamw"]}
+        for t in range(1, 4):
+            grads = {n: obf.rne_f32((rng.standard_normal(s) * 1e-3).astype(np.float32)) for n, s in shp.items()}
+            opt.step(grads, None)
+            ref_mu.step({n: grads[n] for n in r["muon"]})
+            s = adamw_ref.adamw_scalars(AKW["lr"], *AKW["betas"], AKW["eps"], t)
+            p16 = {}
+            for n in r["adamw"]:
+                wd = 0.0 if len(shp[n]) == 1 else AKW["wd"]
+                p, m, v, b = adamw_ref.adamw_step(*st[n], grads[n].reshape(-1), s, wd, "sr", 1234, t,
+                                                  opt.engine.a_off[n])
+                st[n] = [p, m, v]
+                p16[n] = b
+        master, w = opt.master(), opt.weights()
+        for n in r["adamw"]:                                   # AdamW: bit-exact after 3 steps
+            assert np.array_equal(master[n].reshape(-1), st[n][0]), n
+            assert np.array_equal(f32_to_bf16_bits(w[n]).reshape(-1), p16[n]), n
+        for n in r["muon"]:                                    # Muon: update within tolerance
+            a, b = (master[n] - params[n]).ravel(), (ref_mu.w[n] - params[n]).ravel()
+            rel = np.linalg.norm(a - b) / np.linalg.norm(b)
+            assert rel < 0.06, (n, rel)
+        opt.free()
+    finally:
+        anc.set_polar_express(bool(prev))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_zero1_shards_bitwise_equal_single(ctx, world):
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=3)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    grads = S.synthetic_grads_bf16(shp, seed=4)
+
+    def run(rank, w):
+        eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=7,
+                                 rank=rank, world=w, schedule=anc.PE_SCHEDULE, ctx=ctx)
+        for _ in range(2):
+            eng.upload_grads(grads, ctx.stream)
+            eng.step(ctx.stream, exchange=False)
+        ctx.sync()
+        assert ctx.status() == 0
+        bits, _ = eng.download_weights_bits()
+        bits = {n: b.copy() for n, b in bits.items()}
+        res = (bits, eng.master(), {n: eng.owned_range(n) for n in shp})
+        eng.free()
+        return res
+
+    full_bits, full_master, _ = run(0, 1)
+    covered = {n: 0 for n in shp}
+    for r in range(world):
+        bits, master, owned = run(r, world)
+        for n in shp:
+            s, e = owned[n]
+            if e <= s:
+                continue
+            covered[n] += e - s
+            assert np.array_equal(bits[n].reshape(-1)[s:e], full_bits[n].reshape(-1)[s:e]), (r, n)
+            ms, me, flat = master[n]
+            assert (ms, me) == (s, e)
+            assert np.array_equal(flat, full_master[n][2][s:e]), (r, n)
+    for n, s in shp.items():
+        assert covered[n] == int(np.prod(s)), n               # every element owned exactly once

@@ -1,0 +1,123 @@
+"""GPU: the Muon classes against the reference's host Muon restated in the oracle.
+
+Tolerances from tests/kernels/_probe_device_muon.py:63-65,131-133 (after 5 steps the total
+update has cos > 0.99 and rel < 0.06 vs the fp32 host optimizer, for square / wide / tall) and
+tests/training/test_batched_proj_muon.py:71-74 (batched == per-weight, scope == global bitwise)."""
+import numpy as np
+import pytest
+
+import ancora_cutile_b200 as anc
+from ancora_cutile_b200.bf16 import bits_to_f32, f32_to_bf16_bits
+from oracle import muon_ref
+
+pytestmark = pytest.mark.gpu
+SHAPES = {"sq": (256, 256), "wide": (128, 384), "tall": (384, 128)}
+
+
+def cos_rel(a, b):
+    a, b = a.ravel().astype(np.float64), b.ravel().astype(np.float64)
+    return (float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30)),
+            float(np.linalg.norm(a - b) / (np.linalg.norm(b) + 1e-30)))
+
+
+def _setup(rng):
+    P = {n: (rng.standard_normal(s) * 0.02).astype(np.float32) for n, s in SHAPES.items()}
+    Gs = [{n: (rng.standard_normal(s) * 1e-3).astype(np.float32) for n, s in SHAPES.items()} for _ in range(5)]
+    return P, Gs
+
+
+def test_host_api_muon_vs_host_reference(ctx):
+    rng = np.random.default_rng(0)
+    P, Gs = _setup(rng)
+    opt = anc.Muon(P, lr=0.02, momentum=0.95, nesterov=True, ns_steps=5, ctx=ctx)     # Keller default
+    ref = muon_ref.HostMuon(P, schedule=None)
+    for g in Gs:
+        opt.step(g, None)
+        ref.step(g)
+    m = opt.master()
+    for n in P:
+        c, r = cos_rel(m[n] - P[n], ref.w[n] - P[n])
+        assert c > 0.99 and r < 0.06, (n, c, r)
+        assert np.array_equal(f32_to_bf16_bits(opt.weights()[n]), f32_to_bf16_bits(m[n]))   # weights == RNE(master)
+    opt.free()
+
+
+def _resident_weights(ctx, P, G):
+    ws = []
+    for lid, n in enumerate(P):
+        K, N = P[n].shape
+        ws.append(dict(buf=anc.DBuf.zeros((K, N), np.float32, ctx), p32=anc.DBuf(P[n], ctx),
+                       p16=anc.DBuf(f32_to_bf16_bits(P[n]), ctx), G=anc.DBuf(G[n], ctx), K=K, N=N, lid=lid, name=n))
+    return ws
+
+
+def _free(ws):
+    for w in ws:
+        for k in ("buf", "p32", "p16", "G"):
+            w[k].free()
+
+
+def test_batched_equals_per_weight_and_scope_bitwise(ctx):
+    rng = np.random.default_rng(1)
+    P = {f"l{i}.{n}": (rng.standard_normal(s) * 0.02).astype(np.float32)
+         for i in range(3) for n, s in SHAPES.items()}
+    G = {n: (rng.standard_normal(p.shape) * 1e-3).astype(np.float32) for n, p in P.items()}
+    results = []
+    for mode in ("global", "scope1", "chunk2", "per_weight"):
+        ws = _resident_weights(ctx, P, G)
+        for i, w in enumerate(ws):
+            w["lid"] = i // 3
+        if mode == "per_weight":
+            opts = [anc.ResidentMuon(w["p32"], w["p16"], w["K"], w["N"], None, ctx=ctx) for w in ws]
+            for _ in range(3):
+                for o, w in zip(opts, ws):
+                    o.step(w["G"], ctx.stream, 0.02)
+        else:
+            kw = dict(scope=1) if mode == "scope1" else dict(chunk=2) if mode == "chunk2" else {}
+            bp = anc.BatchedProjMuon(ws, **kw, ctx=ctx)
+            for _ in range(3):
+                bp.step(ctx.stream, 0.02)
+            opts = [bp]
+        ctx.sync()
+        assert ctx.status() == 0
+        results.append({w["name"]: (w["p32"].to_numpy(), w["p16"].to_numpy()) for w in ws})
+        for o in opts:
+            o.free()
+        _free(ws)
+    base = results[0]
+    for other in results[1:]:
+        for n in base:
+            assert np.array_equal(base[n][0], other[n][0]), n
+            assert np.array_equal(base[n][1], other[n][1]), n
+
+
+def test_resident_muon_vs_host_reference_pe(ctx):
+    rng = np.random.default_rng(2)
+    P, Gs = _setup(rng)
+    prev = anc.set_polar_express(True)
+    try:
+        ref = muon_ref.HostMuon(P, schedule=muon_ref.PE_SCHEDULE)
+        ws = _resident_weights(ctx, P, Gs[0])
+        bp = anc.BatchedProjMuon(ws, ctx=ctx)
+        for g in Gs:
+            for w in ws:
+                w["G"].upload(g[w["name"]])
+            bp.step(ctx.stream, 0.02)
+            ref.step(g)
+        ctx.sync()
+        for w in ws:
+            n = w["name"]
+            c, r = cos_rel(w["p32"].to_numpy() - P[n], ref.w[n] - P[n])
+            assert c > 0.99 and r < 0.06, (n, c, r)
+            assert np.array_equal(w["p16"].to_numpy(), f32_to_bf16_bits(w["p32"].to_numpy()))
+        bp.free()
+        _free(ws)
+    finally:
+        anc.set_polar_express(bool(prev))
+
+
+def test_misaligned_shape_raises(ctx):
+    with pytest.raises(AssertionError):
+        anc.Muon({"router": np.zeros((1024, 16), np.float32)}, ctx=ctx)
+    with pytest.raises(AssertionError):
+        anc.Muon({"gain": np.zeros((128,), np.float32)}, ctx=ctx)
