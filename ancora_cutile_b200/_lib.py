@@ -80,6 +80,7 @@ SIGNATURES = {
     "anc_muon_momentum": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _i, _vp]),
     "anc_muon_update": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "anc_fro_normalize": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "anc_fro_normalize_static": (_i, [_i, _vp, _vp, _i, _i, _i, _f, _vp]),
     "anc_nccl_load": (_i, [C.c_char_p]),
     "anc_nccl_unique_id": (_i, [_vp]),
     "anc_comm_create": (_i, [_vp, _vp, _i, _i, _pp]),

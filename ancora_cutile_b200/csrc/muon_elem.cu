@@ -9,6 +9,7 @@
 // transposed through a shared-memory tile, which is bit-identical to the untransposed
 // kernel followed by a transpose (reference: _muon_mom_t, _muon_update_cast_t).
 #include <cuda_bf16.h>
+#include <mutex>
 #include "anc_internal.h"
 
 namespace {
@@ -363,6 +364,23 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *o
   return ANC_OK;
 }
 
+// ---- allocation-free Frobenius normalisation -------------------------------------
+// The per-block partial sums of squares live in this file-scope device array instead of a
+// cudaMalloc'ed workspace.  Every GPU that loads the library carries these 256 KiB until the
+// process exits.
+#define ANC_FRO_STATIC_MAX_BLOCKS 65536
+static __device__ __align__(256) float g_fro_static_partials[ANC_FRO_STATIC_MAX_BLOCKS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct StaticScratch {
+  float *partials = nullptr;   // device address of g_fro_static_partials on this device
+  int sm_count = 0;
+};
+StaticScratch g_static[kMaxDevices];
+std::mutex g_static_mu;
+}  // namespace
+
 extern "C" {
 
 int anc_muon_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u, int K,
@@ -379,6 +397,45 @@ int anc_muon_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O, 
   anc_device_guard guard(ctx->device);
   return anc_launch_update(ctx, p32, p16, O, K, N, lr_scale, transposed,
                            anc_pick_stream(ctx, stream));
+}
+
+int anc_fro_normalize_static(int device, uint16_t *X, float *recip, int E, int M, int N, float eps,
+                             void *stream) {
+  ANC_REQUIRE(X && recip, "NULL argument");
+  ANC_REQUIRE(device >= 0 && device < kMaxDevices, "bad device index %d", device);
+  ANC_REQUIRE(E > 0 && M > 0 && N > 0, "bad shape (%d x %d x %d)", E, M, N);
+  ANC_REQUIRE(((size_t)M * N) % kFroBlock == 0, "matrix of %dx%d elements is not a multiple of %d",
+              M, N, kFroBlock);
+  const size_t bpm = ((size_t)M * N) / kFroBlock;
+  const size_t total = (size_t)E * bpm;
+  ANC_REQUIRE(total <= ANC_FRO_STATIC_MAX_BLOCKS,
+              "anc_fro_normalize_static: %zu blocks of %d elements exceed the built-in scratch of %d "
+              "blocks (E*M*N <= 2^30 elements); use anc_fro_normalize",
+              total, kFroBlock, ANC_FRO_STATIC_MAX_BLOCKS);
+  anc_device_guard guard(device);
+  StaticScratch sc;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static[device].partials) {
+      // First call on this device: resolve the array's DEVICE address.  In host code the
+      // symbol's name is only a handle, not something a kernel may dereference.
+      float *ptr = nullptr;
+      ANC_CUDA(cudaGetSymbolAddress((void **)&ptr, g_fro_static_partials));
+      int sms = 0;
+      ANC_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+      g_static[device].sm_count = sms;
+      g_static[device].partials = ptr;
+    }
+    sc = g_static[device];
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t cap = (size_t)sc.sm_count * 8;
+  const int grid = (int)(total < cap ? total : cap);
+  fro_partial_kernel<<<grid, kThreads, 0, st>>>(X, sc.partials, (int)total);
+  ANC_CUDA(cudaGetLastError());
+  fro_scale_kernel<<<grid, kThreads, 0, st>>>(X, sc.partials, recip, (int)bpm, (int)total, eps);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
 }
 
 int anc_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,

@@ -211,6 +211,33 @@ ANC_API int anc_muon_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint1
 ANC_API int anc_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
                               void *stream);
 
+/* Frobenius normalisation that allocates nothing.  No counterpart in the reference.
+ *
+ * Same kernels, same reduction order and therefore the same bits as anc_fro_normalize,
+ * but the per-block partial sums go to a 256 KiB array built into the library's device
+ * image rather than to a cudaMalloc'ed workspace, and no anc_ctx (whose creation
+ * allocates) is needed.  It is for callers that must not enter the CUDA allocator at the
+ * point of the call: a training loop whose device memory is owned entirely by a
+ * framework's caching pool (a raw cudaMalloc there can fail for lack of un-pooled memory
+ * or force a device-wide synchronisation), or a latency-critical step that has to stay
+ * free of the implicit synchronisation cudaMalloc/cudaFree cause.  The caller still
+ * supplies X (E*M rows of N bf16 values, normalised in place) and recip (E floats).
+ *
+ * Limits and rules:
+ *   - E*M*N / 16384 must not exceed 65536 (2^30 elements per call); larger calls are
+ *     rejected with ANC_E_INVALID and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     made current) and remembers it; make that first call outside any stream capture.
+ *   - All calls on one device share the one array.  Nothing in it has to start at zero
+ *     (every slot is written before it is read within a call), but two calls whose
+ *     kernels may overlap on the GPU (different streams, no dependency) would overwrite
+ *     each other's partial sums: keep such calls ordered.
+ *   - Every GPU that loads the library holds the 256 KiB until the process exits.
+ * `device` is the CUDA device ordinal of X; `stream` a stream of that device (NULL = the
+ * legacy default stream). */
+ANC_API int anc_fro_normalize_static(int device, uint16_t *X, float *recip, int E, int M, int N,
+                                     float eps, void *stream);
+
 /* ----------------------------------------------------------------- ZeRO-1 ---- */
 /* No counterpart in the reference (single GPU, ancora README.md:93).  NCCL is
  * opened with dlopen at first use; nccl_path may be NULL (default search). */
