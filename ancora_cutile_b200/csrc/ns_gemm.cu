@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <map>
+#include <stdlib.h>
 #include <vector>
 #include "anc_internal.h"
 
@@ -354,6 +355,323 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+
+// ====================================================================================
+// CTA-pair variant (tcgen05 cta_group::2).  Two CTAs of a 2-CTA cluster compute one
+// 256x256 tile: CTA r owns rows [128r, 128r+128) of the tile (its accumulator lives in its
+// own TMEM) and loads only its half of each operand per K block -- 128 rows of A and 128
+// of the 256 B columns (16 KiB + 16 KiB per stage instead of 16 + 32) -- so the bytes an
+// SM must keep in flight per FLOP drop by a third and six stages fit in shared memory.
+// The leader CTA (cluster rank 0) issues every MMA; both CTAs' TMA loads complete on the
+// leader's "full" barrier; stage release and accumulator-ready signals are multicast
+// tcgen05.commit arrivals on both CTAs' barriers; the peer's epilogue warps arrive on the
+// leader's "accumulator free" barrier through its cluster address.  No TMA load is
+// multicast.
+// ====================================================================================
+constexpr int kStages2 = 5;
+constexpr int kHalfBBytes = 128 * BK * 2;                 // 16 KiB
+constexpr int kStageBytes2 = kABytes + kHalfBBytes;       // 32 KiB
+constexpr int kEpiBoxBytes = 128 * 64 * 2;                // one 128-row x 64-column bf16 box
+constexpr int kEpiBytes = 4 * kEpiBoxBytes;               // 128 x 256 staging tile, 64 KiB
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kEpiBytes + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                                 uint32_t leader_bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+               "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void epi_bar(int id) {   // the 128 epilogue threads only
+  asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+
+// tile_tab entries here are (I | J << 8) in units of 256 rows / 256 columns.
+__global__ void __launch_bounds__(kThreads, 1)
+ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gen_base = smem_raw + (base - raw);
+  const uint32_t epi_base = base + kStages2 * kStageBytes2;      // 64 KiB staging, 1024-aligned
+  uint8_t *epi_gen = gen_base + kStages2 * kStageBytes2;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_gen + kEpiBytes);
+  const uint32_t bar0 = epi_base + kEpiBytes;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + 2 + b); };
+  const uint32_t dfull_bar = bar0 + 8u * (2 * kStages2 + 4);     // axpy operand landed in staging
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages2 + 5);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();          // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(full_bar(s), 1);      // leader's copy is the one in use
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);    // 4 epilogue warps in each of the 2 CTAs (leader's copy in use)
+    }
+    mbar_init(dfull_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // both CTAs' barriers exist before any remote signal
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool nmajor_b = (p.mode == 2);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < p.total_tiles; t += n_pairs) {
+        const int e = t / p.tiles_per_matrix;
+        const uint32_t tt = p.tile_tab[t - e * p.tiles_per_matrix];
+        const int I = tt & 0xFF, J = (tt >> 8) & 0xFF;
+        const int row0 = e * p.M;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+            atomicOr(p.status, ANC_DEV_TIMEOUT_TMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t sa = base + s * kStageBytes2;
+          const uint32_t sb = sa + kABytes;
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (crank == 0) mbar_expect_tx(full_bar(s), 2u * kStageBytes2);   // both CTAs' bytes
+          tma_load_2d_pair(sa, &tmA, kb * BK, row0 + I * 256 + (int)crank * 128, lead_full);
+          if (!nmajor_b) {
+            tma_load_2d_pair(sb, &tmB, kb * BK, row0 + J * 256 + (int)crank * 128, lead_full);
+          } else {
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d_pair(sb + c * (64 * BK * 2), &tmB, J * 256 + (int)crank * 128 + c * 64,
+                               row0 + kb * BK, lead_full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && crank == 0) {
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      // D=f32, A=B=bf16, A K-major, B K- or N-major, N=256, M=256 (pair)
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((nmajor_b ? 1u : 0u) << 16) |
+                             ((256u >> 3) << 17) | ((256u >> 4) << 24);
+      for (int t = pair_id; ok && t < p.total_tiles; t += n_pairs, ++acc_it) {
+        const uint32_t buf = acc_it & 1;
+        const uint32_t aph = (acc_it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) {
+          atomicOr(p.status, ANC_DEV_TIMEOUT_MMA);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 256u;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+            atomicOr(p.status, ANC_DEV_TIMEOUT_MMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes2;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = nmajor_b ? make_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                         : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(s));
+        }
+        if (ok) tc_commit_pair(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, both CTAs)
+    // Global traffic goes through a 128x256 bf16 staging tile in shared memory (four
+    // 128-row x 64-column boxes, 128-byte swizzle): the axpy operand arrives by TMA while
+    // the tile's MMAs still run, each thread combines its row in place, and the result
+    // leaves by TMA store.  Only the mirrored (transposed) blocks of the symmetric phases
+    // are stored from registers.
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const bool elected = (threadIdx.x == 64);
+    uint32_t acc_it = 0;
+    for (int t = pair_id; t < p.total_tiles; t += n_pairs, ++acc_it) {
+      const int e = t / p.tiles_per_matrix;
+      const uint32_t tt = p.tile_tab[t - e * p.tiles_per_matrix];
+      const int I = tt & 0xFF, J = (tt >> 8) & 0xFF;
+      const int i = 2 * I + (int)crank;       // this CTA's 128-row block
+      const int j = 2 * J;                    // first 128-column block
+      // symmetric phases keep the lower 128-blocks only (hb <= i); the upper block of a
+      // diagonal tile is produced by the mirror of its transpose
+      const int nblk = (p.mode == 2 || j + 1 <= i) ? 2 : 1;
+      const uint32_t buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      const int grow0 = e * p.M + i * BM;
+      if (elected) {
+        bulk_wait_read0();                    // previous tile's stores no longer read staging
+        if (p.mode != 0) {
+          mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
+          for (int b = 0; b < 2 * nblk; ++b)
+            tma_load_2d(epi_base + b * kEpiBoxBytes, &tmD, j * 128 + b * 64, grow0, dfull_bar);
+        }
+      }
+      epi_bar(2);                             // staging is free for this tile
+      bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
+      if (ok && p.mode != 0) ok = mbar_wait(dfull_bar, acc_it & 1, abort_flag);
+      if (!ok) {
+        if (lane == 0) atomicOr(p.status, ANC_DEV_TIMEOUT_EPI);
+        *abort_flag = 1;
+      } else {
+        tc_fence_after();
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+        uint8_t *my_row = epi_gen + r * 128;
+        for (int cc = 0; cc < 4 * nblk; ++cc) {
+          uint32_t v[32];
+          tc_ld32(taddr0 + cc * 32, v);
+          tc_wait_ld();
+          // this thread's 32 columns sit in box cc/2 as four 16-byte pieces, swizzled by row
+          uint8_t *box_row = my_row + (cc >> 1) * kEpiBoxBytes;
+          const int c16 = (cc & 1) * 4;
+          uint32_t h[16];
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            uint4 *slot = reinterpret_cast<uint4 *>(box_row + (((c16 + k4) ^ (r & 7)) << 4));
+            float f[8];
+            if (p.mode == 0) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[k4 * 8 + k]);
+            } else {
+              const uint4 d = *slot;
+              const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float dlo = __uint_as_float(dw[k] << 16);
+                const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
+                f[2 * k] = __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(p.alpha, dlo));
+                f[2 * k + 1] =
+                    __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(p.alpha, dhi));
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) h[k4 * 4 + k] = pack_bf16(f[2 * k], f[2 * k + 1]);
+            *slot = make_uint4(h[k4 * 4], h[k4 * 4 + 1], h[k4 * 4 + 2], h[k4 * 4 + 3]);
+          }
+          const int hb = j + (cc >> 2);
+          if (p.mode != 2 && hb < i) {
+            const int col = j * 128 + cc * 32;
+            uint16_t *mcol = p.C + ((size_t)e * p.M + (size_t)col) * p.ldc + (size_t)i * BM + r;
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              mcol[(size_t)k * p.ldc] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
+          }
+        }
+        // accumulator fully read: hand the TMEM buffer back before the stores go out
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        fence_async_smem();                   // staging writes visible to the TMA store
+      }
+      epi_bar(1);                             // every row of the staging tile is final
+      if (*abort_flag) break;                 // uniform: the flag was set before the barrier
+      if (elected) {
+        for (int b = 0; b < 2 * nblk; ++b)
+          tma_store_2d(&tmC, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
+        bulk_commit();
+      }
+    }
+    if (elected) bulk_wait0();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // the peer's shared memory and barriers stay valid until here
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 // ---- host side -------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -407,22 +725,29 @@ struct TileTab {
 struct GemmCache {
   std::map<uint64_t, TileTab> tabs;
   bool attr_set = false;
+  bool attr2_set = false;
 };
 std::map<anc_ctx *, GemmCache *> g_caches;
 
 // Tile list of one matrix.  sym: lower-triangular 128-blocks of an (mb x mb) grid packed
 // into 256-wide tiles; else the full (mb x nb) grid.
-int get_tile_tab(anc_ctx *ctx, bool sym, int mb, int nb, TileTab *out) {
+int get_tile_tab(anc_ctx *ctx, bool sym, bool pair, int mb, int nb, TileTab *out) {
   GemmCache *&gc = g_caches[ctx];
   if (!gc) gc = new GemmCache();
-  const uint64_t key = ((uint64_t)(sym ? 1 : 0) << 40) | ((uint64_t)mb << 20) | (uint64_t)nb;
+  const uint64_t key = ((uint64_t)(sym ? 1 : 0) << 40) | ((uint64_t)(pair ? 1 : 0) << 41) |
+                       ((uint64_t)mb << 20) | (uint64_t)nb;
   auto it = gc->tabs.find(key);
   if (it != gc->tabs.end()) {
     *out = it->second;
     return ANC_OK;
   }
   std::vector<uint32_t> tab;
-  for (int i = 0; i < mb; ++i) {
+  if (pair) {
+    // units of 256 rows x 256 columns; sym keeps J <= I
+    for (int i = 0; i < mb / 2; ++i)
+      for (int j = 0; j < (sym ? i + 1 : nb / 2); ++j) tab.push_back((uint32_t)i | ((uint32_t)j << 8));
+  }
+  for (int i = 0; !pair && i < mb; ++i) {
     if (sym) {
       for (int j = 0; j <= i; j += 2) {
         const int w = (j + 1 <= i) ? 2 : 1;
@@ -474,8 +799,12 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
     rc = make_map(&tmB, P, (uint64_t)E * M, (uint64_t)Kdim, 128);
   }
   if (rc) return rc;
+  // CTA pairs need 256-row tiles (and 256-column tiles in the apply phase)
+  const char *env = getenv("ANCORA_NS_CTA_PAIR");
+  const bool pair = !(env && env[0] == '0') && M % 256 == 0 && (mode != 2 || N % 256 == 0) &&
+                    ctx->sm_count >= 2;
   TileTab tt;
-  rc = get_tile_tab(ctx, mode != 2, mb, mode == 2 ? N / 128 : mb, &tt);
+  rc = get_tile_tab(ctx, mode != 2, pair, mb, mode == 2 ? N / 128 : mb, &tt);
   if (rc) return rc;
   GemmCache *gc = g_caches[ctx];
   if (!gc->attr_set) {
@@ -497,6 +826,34 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
   p.mode = mode;
   p.alpha = alpha;
   p.beta = beta;
+  if (pair) {
+    if (!gc->attr2_set) {
+      ANC_CUDA(cudaFuncSetAttribute(ns_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes2));
+      gc->attr2_set = true;
+    }
+    int pairs = ctx->sm_count / 2;
+    if (p.total_tiles < pairs) pairs = p.total_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes2;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CUtensorMap tmC, tmD;
+    rc = make_map(&tmC, C, (uint64_t)E * M, (uint64_t)p.ldc, 128);
+    if (rc) return rc;
+    rc = make_map(&tmD, mode == 0 ? (const void *)C : (const void *)p.D, (uint64_t)E * M, (uint64_t)p.ldc, 128);
+    if (rc) return rc;
+    ANC_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_pair_kernel, tmA, tmB, tmC, tmD, p));
+    return ANC_OK;
+  }
   int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
   ns_gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, p);
   ANC_CUDA(cudaGetLastError());

@@ -68,7 +68,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.005)
 
     def start(self):
         if self.nv:
@@ -83,11 +83,19 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def workload_shapes(name):
+def workload_shapes(name, layers=None, vocab=None):
+    """layers / vocab shrink the model for profiler captures; a run that sets them is not
+    the benchmark configuration and says so in config.workload."""
     from ancora_cutile_b200 import shapes
+    kw = {}
+    if layers:
+        kw["n_layers"] = layers
+    if vocab:
+        kw["vocab"] = vocab
+    tag = f" REDUCED for profiling: {kw}" if kw else ""
     if name == "qwen3":
-        return shapes.qwen3_0_6b_shapes(), "qwen3-0.6b hybrid optimizer step (28 layers, d=1024, ffn=3072, vocab=151936)"
-    return shapes.moe_family_shapes(), "moe-family hybrid optimizer step (24 layers, 16x(768x1024) experts per MoE layer)"
+        return shapes.qwen3_0_6b_shapes(**kw), "qwen3-0.6b hybrid optimizer step (28 layers, d=1024, ffn=3072, vocab=151936)" + tag
+    return shapes.moe_family_shapes(**kw), "moe-family hybrid optimizer step (24 layers, 16x(768x1024) experts per MoE layer)" + tag
 
 
 def route(shp):
@@ -158,12 +166,14 @@ def main():
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "moe"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--layers", type=int, default=None, help="profiling only: fewer layers")
+    ap.add_argument("--vocab", type=int, default=None, help="profiling only: smaller vocabulary")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    shp, wl_name = workload_shapes(args.workload)
+    shp, wl_name = workload_shapes(args.workload, args.layers, args.vocab)
     muon_names = route(shp)
     total_params = int(sum(int(np.prod(s)) for s in shp.values()))
     config = {"workload": wl_name, "params": total_params, "muon_matrices": len(muon_names),
