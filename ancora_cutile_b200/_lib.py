@@ -63,6 +63,9 @@ SIGNATURES = {
     "anc_event_sync": (_i, [_vp]),
     "anc_event_elapsed_ms": (_i, [_vp, _vp, C.POINTER(_f)]),
     "anc_event_destroy": (_i, [_vp]),
+    "anc_stream_create": (_i, [_vp, _pp]),
+    "anc_stream_destroy": (_i, [_vp, _vp]),
+    "anc_stream_wait_event": (_i, [_vp, _vp]),
     "anc_flush_l2": (_i, [_vp, _vp]),
     "anc_adamw_plan_create": (_i, [_vp, C.POINTER(AdamWTensor), _i, _i, _pp]),
     "anc_adamw_plan_set_range": (_i, [_vp, _u64, _u64]),
@@ -71,6 +74,9 @@ SIGNATURES = {
     "anc_adamw_plan_destroy": (_i, [_vp]),
     "anc_muon_plan_create": (_i, [_vp, C.POINTER(MuonWeight), _i, _i, _i, _i, _pp]),
     "anc_muon_step": (_i, [_vp, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
+    "anc_muon_plan_num_chunks": (_i, [_vp, C.POINTER(_i)]),
+    "anc_muon_plan_chunk_info": (_i, [_vp, _i, C.POINTER(C.c_int32)]),
+    "anc_muon_step_chunk": (_i, [_vp, _i, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
     "anc_muon_plan_set_timing": (_i, [_vp, _i]),
     "anc_muon_plan_last_timing": (_i, [_vp, C.POINTER(_f), C.POINTER(_d), C.POINTER(_i)]),
     "anc_muon_plan_scratch_bytes": (_i, [_vp, C.POINTER(_u64)]),
@@ -88,6 +94,11 @@ SIGNATURES = {
     "anc_comm_allgather_bf16": (_i, [_vp, _vp, _u64, _vp]),
     "anc_comm_bcast_segments": (_i, [_vp, _pp, C.POINTER(_u64), C.POINTER(_i), _i, _vp]),
     "anc_comm_barrier": (_i, [_vp, _vp]),
+    "anc_ipc_export_mem": (_i, [_vp, _vp, _vp]),
+    "anc_ipc_open_mem": (_i, [_vp, _vp, _pp]),
+    "anc_ipc_close_mem": (_i, [_vp, _vp]),
+    "anc_p2p_signal": (_i, [_vp, _vp, C.c_uint32, _vp]),
+    "anc_p2p_wait_flags": (_i, [_vp, _vp, _i, _i, C.c_uint32, _vp]),
 }
 
 _lib = None

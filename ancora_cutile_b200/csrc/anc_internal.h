@@ -4,6 +4,7 @@
 #include <stdint.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 #include "../../include/ancora_b200.h"
 
 struct anc_ctx {
@@ -27,6 +28,7 @@ struct anc_upd_entry { float *p32; uint16_t *p16; int slot, K, N, tr; };
 #define ANC_DEV_TIMEOUT_MMA 0x2u
 #define ANC_DEV_TIMEOUT_EPI 0x4u
 #define ANC_DEV_BAD_INDEX 0x8u       // a table index failed its bounds check
+#define ANC_DEV_TIMEOUT_PEER 0x10u   // a peer rank's completion flag never arrived
 
 void anc_set_error(const char *fmt, ...);
 int anc_cuda_fail(cudaError_t e, const char *what);
@@ -71,10 +73,17 @@ int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int
                              cudaStream_t st);
 int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
                               int elems_per_w, int grad_dtype, float momentum, int nesterov,
-                              cudaStream_t st);
+                              float *partial, cudaStream_t st);
+int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
+                            float eps, cudaStream_t st);
+int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int E, int M, int N,
+                           cudaStream_t st);
 int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *obase, int n_w,
                             int elems_per_w, float lr_scale_wide, float lr_scale_tall,
                             cudaStream_t st);
+// mscale (nullable): per-matrix factor r[e] folded into the epilogue -- mode 0 stores
+// RNE(r^2 * acc), mode 2 stores RNE((alpha*r)*Q + (beta*r)*acc); mode 1 ignores it.
 int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
-                       int E, int M, int N, float alpha, float beta, cudaStream_t st);
+                       int E, int M, int N, float alpha, float beta, const float *mscale,
+                       cudaStream_t st);
 void anc_gemm_cache_destroy(anc_ctx *ctx);

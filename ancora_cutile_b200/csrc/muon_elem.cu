@@ -37,43 +37,58 @@ __device__ __forceinline__ uint32_t rne16(float x) {
 }
 __device__ __forceinline__ float bf16_f32(uint32_t h) { return __uint_as_float(h << 16); }
 
-// One 64x64 tile of one weight.  Thread t: columns 4*(t%16)..+3, rows t/16 + 16*k.
+// One 64x64 tile of one weight.  Thread t: columns 8*(t%8)..+7, rows t/8 and t/8 + 32,
+// 128-bit accesses.  Returns this thread's sum of squares of the bf16-rounded u values
+// (added in element order: first row left to right, then the second row).
 template <bool kGradF32>
-__device__ __forceinline__ void momentum_tile(const MomW &w, uint16_t *xbase, int ti, int tj, float mu,
-                                              int nesterov, uint16_t (*sm)[kTile + kPad]) {
+__device__ __forceinline__ float momentum_tile(const MomW &w, uint16_t *xbase, int ti, int tj, float mu,
+                                               int nesterov, uint16_t (*sm)[kTile + kPad]) {
   uint16_t *wx = xbase + (size_t)w.slot * w.K * w.N;
-  const int c4 = (threadIdx.x & 15) * 4;
-  const int r0 = threadIdx.x >> 4;
-  const int col = tj * kTile + c4;
+  const int c8 = (threadIdx.x & 7) * 8;
+  const int r0 = threadIdx.x >> 3;
+  const int col = tj * kTile + c8;
+  // A weight stored in its Newton-Schulz orientation is a flat copy: its "tile" is 4096
+  // contiguous elements (streams like a memcpy).  A tall weight needs 64x64 tiles for the
+  // transposed store.
+  const size_t flat0 = ((size_t)ti * (w.N / kTile) + tj) * (kTile * kTile) + (size_t)threadIdx.x * 8;
+  float ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int rl = r0 + 16 * k;
-    const size_t idx = (size_t)(ti * kTile + rl) * w.N + col;
-    const float4 b = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx));
-    float g[4];
+  for (int k = 0; k < 2; ++k) {
+    const int rl = r0 + 32 * k;
+    const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + col : flat0 + (size_t)k * (kThreads * 8);
+    const float4 b0 = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx));
+    const float4 b1 = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx) + 1);
+    float g[8];
     if constexpr (kGradF32) {
-      const float4 gv = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx));
-      g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+      const float4 g0 = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx));
+      const float4 g1 = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx) + 1);
+      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
     } else {
-      const uint2 gv = __ldcs(reinterpret_cast<const uint2 *>((const uint16_t *)w.g + idx));
-      g[0] = __uint_as_float(gv.x << 16); g[1] = __uint_as_float(gv.x & 0xFFFF0000u);
-      g[2] = __uint_as_float(gv.y << 16); g[3] = __uint_as_float(gv.y & 0xFFFF0000u);
-    }
-    const float bb[4] = {b.x, b.y, b.z, b.w};
-    float nb[4];
-    uint32_t h[4];
+      const uint4 gv = __ldcs(reinterpret_cast<const uint4 *>((const uint16_t *)w.g + idx));
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 4; ++j) {
+        g[2 * j] = __uint_as_float(gw[j] << 16);
+        g[2 * j + 1] = __uint_as_float(gw[j] & 0xFFFF0000u);
+      }
+    }
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float nb[8];
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
       nb[j] = __fadd_rn(__fmul_rn(mu, bb[j]), g[j]);
       const float u = nesterov ? __fadd_rn(g[j], __fmul_rn(mu, nb[j])) : nb[j];
       h[j] = rne16(u);
+      const float ur = bf16_f32(h[j]);
+      ss = __fadd_rn(ss, __fmul_rn(ur, ur));
     }
     __stcs(reinterpret_cast<float4 *>(w.buf + idx), make_float4(nb[0], nb[1], nb[2], nb[3]));
-    if (!w.tr) {
-      *reinterpret_cast<uint2 *>(wx + idx) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-    } else {
-      *reinterpret_cast<uint2 *>(&sm[rl][c4]) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-    }
+    __stcs(reinterpret_cast<float4 *>(w.buf + idx) + 1, make_float4(nb[4], nb[5], nb[6], nb[7]));
+    const uint4 pk = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16),
+                                h[6] | (h[7] << 16));
+    if (!w.tr) *reinterpret_cast<uint4 *>(wx + idx) = pk;
+    else *reinterpret_cast<uint4 *>(&sm[rl][c8]) = pk;
   }
   if (w.tr) {
     __syncthreads();
@@ -89,14 +104,16 @@ __device__ __forceinline__ void momentum_tile(const MomW &w, uint16_t *xbase, in
     reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     __syncthreads();
   }
+  return ss;
 }
 
 __device__ __forceinline__ void update_tile(const UpdW &w, const uint16_t *obase, float lr_scale,
                                             int ti, int tj, uint16_t (*sm)[kTile + kPad]) {
   const uint16_t *wo = obase + (size_t)w.slot * w.K * w.N;
-  const int c4 = (threadIdx.x & 15) * 4;
-  const int r0 = threadIdx.x >> 4;
-  const int col = tj * kTile + c4;
+  const int c8 = (threadIdx.x & 7) * 8;
+  const int r0 = threadIdx.x >> 3;
+  const int col = tj * kTile + c8;
+  const size_t flat0 = ((size_t)ti * (w.N / kTile) + tj) * (kTile * kTile) + (size_t)threadIdx.x * 8;
   if (w.tr) {
     // stage O^T tile: source rows = columns of the weight tile
     const int oc = threadIdx.x >> 2;
@@ -109,31 +126,59 @@ __device__ __forceinline__ void update_tile(const UpdW &w, const uint16_t *obase
     __syncthreads();
   }
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int rl = r0 + 16 * k;
-    const size_t idx = (size_t)(ti * kTile + rl) * w.N + col;
-    const float4 p = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
-    float o[4];
+  for (int k = 0; k < 2; ++k) {
+    const int rl = r0 + 32 * k;
+    const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + col : flat0 + (size_t)k * (kThreads * 8);
+    const float4 p0 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
+    const float4 p1 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx) + 1);
+    float o[8];
     if (!w.tr) {
-      const uint2 ov = *reinterpret_cast<const uint2 *>(wo + idx);
-      o[0] = __uint_as_float(ov.x << 16); o[1] = __uint_as_float(ov.x & 0xFFFF0000u);
-      o[2] = __uint_as_float(ov.y << 16); o[3] = __uint_as_float(ov.y & 0xFFFF0000u);
+      const uint4 ov = *reinterpret_cast<const uint4 *>(wo + idx);
+      const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[2 * j] = __uint_as_float(ow[j] << 16);
+        o[2 * j + 1] = __uint_as_float(ow[j] & 0xFFFF0000u);
+      }
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = bf16_f32(sm[c4 + j][rl]);
+      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][rl]);
     }
-    const float pp[4] = {p.x, p.y, p.z, p.w};
-    float pn[4];
-    uint32_t h[4];
+    const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float pn[8];
+    uint32_t h[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       pn[j] = __fsub_rn(pp[j], __fmul_rn(lr_scale, o[j]));
       h[j] = rne16(pn[j]);
     }
     __stcs(reinterpret_cast<float4 *>(w.p32 + idx), make_float4(pn[0], pn[1], pn[2], pn[3]));
-    *reinterpret_cast<uint2 *>(w.p16 + idx) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    __stcs(reinterpret_cast<float4 *>(w.p32 + idx) + 1, make_float4(pn[4], pn[5], pn[6], pn[7]));
+    *reinterpret_cast<uint4 *>(w.p16 + idx) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16),
+                                                         h[4] | (h[5] << 16), h[6] | (h[7] << 16));
   }
   if (w.tr) __syncthreads();
+}
+
+__device__ __forceinline__ float warp_tree_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// Sum of one tile over the CTA in a fixed order: thread -> warp shuffle tree -> the 8 warp
+// sums added in warp order by thread 0.
+__device__ __forceinline__ void tile_sumsq_store(float ss, float *dst, float *wsum) {
+  ss = warp_tree_sum_f(ss);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = wsum[0];
+#pragma unroll
+    for (int k = 1; k < kThreads / 32; ++k) t = __fadd_rn(t, wsum[k]);
+    *dst = t;
+  }
+  __syncthreads();
 }
 
 // Table-driven launches: every weight in the table has the same K*N, hence the same
@@ -141,15 +186,38 @@ __device__ __forceinline__ void update_tile(const UpdW &w, const uint16_t *obase
 template <bool kGradF32>
 __global__ void __launch_bounds__(kThreads)
 momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int tiles_per_w, float mu,
-                int nesterov) {
+                int nesterov, float *__restrict__ partial) {
+  // partial[slot * tiles_per_w + tile] = sum of squares of that 64x64 tile of bf16 u
   __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ float wsum[kThreads / 32];
   const int total = n_w * tiles_per_w;
   for (int b = blockIdx.x; b < total; b += gridDim.x) {
     const int wi = b / tiles_per_w;
     const int t = b - wi * tiles_per_w;
     const MomW w = table[wi];
     const int tn = w.N / kTile;
-    momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+    const float ss = momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+    if (partial) tile_sumsq_store(ss, partial + (size_t)w.slot * tiles_per_w + t, wsum);
+  }
+}
+
+// recip[e] = 1 / (sqrt(sum of the matrix's tile partials) + eps): one CTA per matrix,
+// thread-strided partial sums in index order, then the fixed tree.
+__global__ void __launch_bounds__(kThreads)
+fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip, int per_matrix,
+                    float eps) {
+  __shared__ float wsum[kThreads / 32];
+  const float *pp = partial + (size_t)blockIdx.x * per_matrix;
+  float acc = 0.f;
+  for (int k = threadIdx.x; k < per_matrix; k += kThreads) acc = __fadd_rn(acc, pp[k]);
+  acc = warp_tree_sum_f(acc);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = wsum[0];
+#pragma unroll
+    for (int k = 1; k < kThreads / 32; ++k) t = __fadd_rn(t, wsum[k]);
+    recip[blockIdx.x] = __fdiv_rn(1.0f, __fadd_rn(__fsqrt_rn(t), eps));
   }
 }
 
@@ -177,7 +245,7 @@ momentum_one_kernel(MomW w, uint16_t *xbase, float mu, int nesterov) {
   const int tn = w.N / kTile;
   const int total = (w.K / kTile) * tn;
   for (int t = blockIdx.x; t < total; t += gridDim.x)
-    momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+    (void)momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -336,17 +404,37 @@ int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int
 static_assert(sizeof(anc_mom_entry) == sizeof(MomW), "table layout");
 static_assert(sizeof(anc_upd_entry) == sizeof(UpdW), "table layout");
 
+int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
+                            float eps, cudaStream_t st) {
+  (void)ctx;
+  if (E <= 0) return ANC_OK;
+  fro_finalize_kernel<<<E, kThreads, 0, st>>>(partial, recip, per_matrix, eps);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
+// Per-block sums of squares of packed bf16 matrices (blocks of 16384 elements) into `partial`.
+int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int E, int M, int N,
+                           cudaStream_t st) {
+  const size_t total = (size_t)E * (((size_t)M * N) / kFroBlock);
+  int grid = (int)(total < (size_t)ctx->sm_count * 8 ? total : (size_t)ctx->sm_count * 8);
+  if (grid == 0) return ANC_OK;
+  fro_partial_kernel<<<grid, kThreads, 0, st>>>(X, partial, (int)total);
+  ANC_CUDA(cudaGetLastError());
+  return ANC_OK;
+}
+
 int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
                               int elems_per_w, int grad_dtype, float momentum, int nesterov,
-                              cudaStream_t st) {
+                              float *partial, cudaStream_t st) {
   const int tpw = elems_per_w / (kTile * kTile);
   const long long total = (long long)n_w * tpw;
   int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
   if (grid == 0) return ANC_OK;
   if (grad_dtype == ANC_GRAD_F32)
-    momentum_kernel<true><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov);
+    momentum_kernel<true><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov, partial);
   else
-    momentum_kernel<false><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov);
+    momentum_kernel<false><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov, partial);
   ANC_CUDA(cudaGetLastError());
   return ANC_OK;
 }

@@ -37,6 +37,7 @@ struct anc_muon_plan {
   std::vector<Group> groups;
   uint16_t *X = nullptr, *Y = nullptr, *A = nullptr, *B = nullptr;
   float *recip = nullptr;
+  float *partial = nullptr;       // per-tile sums of squares written by the momentum kernel
   uint64_t scratch_bytes = 0;
   bool timing = false;
   std::vector<TimedSpan> spans;
@@ -44,15 +45,19 @@ struct anc_muon_plan {
   int last_launches = 0;
 };
 
+// The chain on an UN-normalised X: the Frobenius factor r[e] = recip[e] enters through the
+// epilogues of the first iteration (A = r^2 X X^T, Y = (a r) X + r (B X)), which equals the
+// chain on r*X without ever writing r*X back to memory.
 static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16_t *&Y, int E, int M,
-                    int N, int steps, const float *coeffs, cudaStream_t st) {
+                    int N, int steps, const float *coeffs, const float *recip, cudaStream_t st) {
   for (int k = 0; k < steps; ++k) {
     const float a = coeffs[3 * k], b = coeffs[3 * k + 1], c = coeffs[3 * k + 2];
-    int rc = anc_launch_ns_gemm(ctx, 0, X, nullptr, A, E, M, N, 0.f, 1.f, st);
+    const float *ms = (k == 0) ? recip : nullptr;
+    int rc = anc_launch_ns_gemm(ctx, 0, X, nullptr, A, E, M, N, 0.f, 1.f, ms, st);
     if (rc) return rc;
-    rc = anc_launch_ns_gemm(ctx, 1, A, nullptr, B, E, M, N, b, c, st);
+    rc = anc_launch_ns_gemm(ctx, 1, A, nullptr, B, E, M, N, b, c, nullptr, st);
     if (rc) return rc;
-    rc = anc_launch_ns_gemm(ctx, 2, B, X, Y, E, M, N, a, 1.f, st);
+    rc = anc_launch_ns_gemm(ctx, 2, B, X, Y, E, M, N, a, 1.f, ms, st);
     if (rc) return rc;
     std::swap(X, Y);
   }
@@ -64,7 +69,8 @@ static void plan_free(anc_muon_plan *pl) {
     if (g.d_mom) cudaFree(g.d_mom);
     if (g.d_upd) cudaFree(g.d_upd);
   }
-  for (void *p : {(void *)pl->X, (void *)pl->Y, (void *)pl->A, (void *)pl->B, (void *)pl->recip})
+  for (void *p : {(void *)pl->X, (void *)pl->Y, (void *)pl->A, (void *)pl->B, (void *)pl->recip,
+                  (void *)pl->partial})
     if (p) cudaFree(p);
   for (auto &s : pl->spans) {
     cudaEventDestroy(s.a);
@@ -146,23 +152,41 @@ int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_wei
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->A, ae * 2);
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->B, ae * 2);
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->recip, emax * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial, (xe / 4096) * sizeof(float));
     if (e != cudaSuccess) {
       plan_free(pl);
       return anc_cuda_fail(e, "muon scratch");
     }
-    pl->scratch_bytes = 4 * xe + 4 * ae + emax * sizeof(float);
+    pl->scratch_bytes = 4 * xe + 4 * ae + emax * sizeof(float) + (xe / 4096) * sizeof(float);
   }
   *out = pl;
   return ANC_OK;
 }
 
-int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, int ns_steps,
-                  const float *coeffs, float eps, void *stream) {
-  ANC_REQUIRE(pl && (coeffs || ns_steps == 0), "NULL argument");
-  ANC_REQUIRE(ns_steps >= 0 && ns_steps <= 64, "bad ns_steps %d", ns_steps);
+}  // extern "C"
+
+namespace {
+
+struct ChunkRef {
+  int group, w0, count;
+};
+
+// Chunks in execution order: shape groups in order of first appearance, each cut into
+// batches of at most max_batch matrices.
+std::vector<ChunkRef> plan_chunks(const anc_muon_plan *pl) {
+  std::vector<ChunkRef> out;
+  for (size_t gi = 0; gi < pl->groups.size(); ++gi) {
+    const int total = (int)pl->groups[gi].widx.size();
+    const int cap = pl->max_batch > 0 ? std::min(pl->max_batch, total) : total;
+    for (int w0 = 0; w0 < total; w0 += cap) out.push_back({(int)gi, w0, std::min(cap, total - w0)});
+  }
+  return out;
+}
+
+int step_chunk(anc_muon_plan *pl, const ChunkRef &c, double lr, float momentum, int nesterov,
+               int ns_steps, const float *coeffs, float eps, cudaStream_t st) {
   anc_ctx *ctx = pl->ctx;
-  anc_device_guard guard(ctx->device);
-  cudaStream_t st = anc_pick_stream(ctx, stream);
+  Group &g = pl->groups[c.group];
   auto begin_span = [&](int phase) {
     if (!pl->timing) return;
     TimedSpan sp;
@@ -176,39 +200,81 @@ int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, in
     if (!pl->timing) return;
     cudaEventRecord(pl->spans.back().b, st);
   };
-  for (auto &g : pl->groups) {
-    const int total = (int)g.widx.size();
-    const int cap = pl->max_batch > 0 ? std::min(pl->max_batch, total) : total;
-    const int epw = g.M * g.Nn;
-    // lr * sqrt(max(1, K/N)) in double, then one float32 rounding (ancora/optim/muon.py:176,200)
-    const float scale_wide = (float)(lr * 1.0);
-    const float scale_tall = (float)(lr * g.scale_tall);
-    for (int w0 = 0; w0 < total; w0 += cap) {
-      const int E = std::min(cap, total - w0);
-      uint16_t *X = pl->X, *Y = pl->Y;
-      begin_span(0);
-      int rc = anc_launch_momentum_group(ctx, g.d_mom + w0, X, E, epw, pl->grad_dtype, momentum,
-                                         nesterov, st);
-      end_span();
-      if (rc) return rc;
-      begin_span(1);
-      rc = anc_launch_fro_normalize(ctx, X, pl->recip, E, g.M, g.Nn, eps, st);
-      end_span();
-      if (rc) return rc;
-      begin_span(2);
-      rc = ns_chain(ctx, X, pl->A, pl->B, Y, E, g.M, g.Nn, ns_steps, coeffs, st);
-      end_span();
-      if (rc) return rc;
-      pl->last_flops += (double)E * ns_steps *
-                        (4.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M);
-      pl->last_launches += 3 * ns_steps;
-      begin_span(3);
-      rc = anc_launch_update_group(ctx, g.d_upd + w0, X, E, epw, scale_wide, scale_tall, st);
-      end_span();
-      if (rc) return rc;
-    }
+  const int epw = g.M * g.Nn;
+  // lr * sqrt(max(1, K/N)) in double, then one float32 rounding (ancora/optim/muon.py:176,200)
+  const float scale_wide = (float)(lr * 1.0);
+  const float scale_tall = (float)(lr * g.scale_tall);
+  const int E = c.count;
+  uint16_t *X = pl->X, *Y = pl->Y;
+  begin_span(0);
+  int rc = anc_launch_momentum_group(ctx, g.d_mom + c.w0, X, E, epw, pl->grad_dtype, momentum, nesterov,
+                                     pl->partial, st);
+  end_span();
+  if (rc) return rc;
+  begin_span(1);
+  if (ns_steps > 0)   // 1/(||u||_F + eps) per matrix from the momentum kernel's tile sums
+    rc = anc_launch_fro_finalize(ctx, pl->partial, pl->recip, E, epw / 4096, eps, st);
+  else                // no iteration to fold the factor into: normalise in place
+    rc = anc_launch_fro_normalize(ctx, X, pl->recip, E, g.M, g.Nn, eps, st);
+  end_span();
+  if (rc) return rc;
+  begin_span(2);
+  rc = ns_chain(ctx, X, pl->A, pl->B, Y, E, g.M, g.Nn, ns_steps, coeffs, pl->recip, st);
+  end_span();
+  if (rc) return rc;
+  pl->last_flops +=
+      (double)E * ns_steps * (4.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M);
+  pl->last_launches += 3 * ns_steps;
+  begin_span(3);
+  rc = anc_launch_update_group(ctx, g.d_upd + c.w0, X, E, epw, scale_wide, scale_tall, st);
+  end_span();
+  return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, int ns_steps,
+                  const float *coeffs, float eps, void *stream) {
+  ANC_REQUIRE(pl && (coeffs || ns_steps == 0), "NULL argument");
+  ANC_REQUIRE(ns_steps >= 0 && ns_steps <= 64, "bad ns_steps %d", ns_steps);
+  anc_device_guard guard(pl->ctx->device);
+  cudaStream_t st = anc_pick_stream(pl->ctx, stream);
+  for (const ChunkRef &c : plan_chunks(pl)) {
+    int rc = step_chunk(pl, c, lr, momentum, nesterov, ns_steps, coeffs, eps, st);
+    if (rc) return rc;
   }
   return ANC_OK;
+}
+
+int anc_muon_plan_num_chunks(anc_muon_plan *pl, int *n) {
+  ANC_REQUIRE(pl && n, "NULL argument");
+  *n = (int)plan_chunks(pl).size();
+  return ANC_OK;
+}
+
+int anc_muon_plan_chunk_info(anc_muon_plan *pl, int chunk, int32_t info[4]) {
+  ANC_REQUIRE(pl && info, "NULL argument");
+  std::vector<ChunkRef> cs = plan_chunks(pl);
+  ANC_REQUIRE(chunk >= 0 && chunk < (int)cs.size(), "chunk %d out of range", chunk);
+  const Group &g = pl->groups[cs[chunk].group];
+  info[0] = g.widx[cs[chunk].w0];   // index (among this plan's weights, in registration order)
+  info[1] = cs[chunk].count;
+  info[2] = g.M;
+  info[3] = g.Nn;
+  return ANC_OK;
+}
+
+int anc_muon_step_chunk(anc_muon_plan *pl, int chunk, double lr, float momentum, int nesterov,
+                        int ns_steps, const float *coeffs, float eps, void *stream) {
+  ANC_REQUIRE(pl && (coeffs || ns_steps == 0), "NULL argument");
+  ANC_REQUIRE(ns_steps >= 0 && ns_steps <= 64, "bad ns_steps %d", ns_steps);
+  std::vector<ChunkRef> cs = plan_chunks(pl);
+  ANC_REQUIRE(chunk >= 0 && chunk < (int)cs.size(), "chunk %d out of range", chunk);
+  anc_device_guard guard(pl->ctx->device);
+  return step_chunk(pl, cs[chunk], lr, momentum, nesterov, ns_steps, coeffs, eps,
+                    anc_pick_stream(pl->ctx, stream));
 }
 
 int anc_muon_plan_set_timing(anc_muon_plan *pl, int on) {
@@ -260,10 +326,24 @@ int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t
   ANC_REQUIRE(M % 128 == 0 && N % 128 == 0, "NS shape (%d,%d) must be multiples of 128", M, N);
   anc_device_guard guard(ctx->device);
   cudaStream_t st = anc_pick_stream(ctx, stream);
-  int rc = anc_launch_fro_normalize(ctx, X, recip, E, M, N, eps, st);
+  if (steps == 0) return anc_launch_fro_normalize(ctx, X, recip, E, M, N, eps, st);
+  // block sums of squares -> recip; the factor itself is applied inside the first iteration
+  const size_t bpm = ((size_t)M * N) / 16384;
+  const size_t need = (size_t)E * bpm * sizeof(float);
+  if (need > ctx->work_bytes) {
+    ANC_CUDA(cudaStreamSynchronize(st));
+    ANC_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->d_work) cudaFree(ctx->d_work);
+    ctx->d_work = nullptr;
+    ctx->work_bytes = need * 2;
+    ANC_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
+  }
+  int rc = anc_launch_fro_partial(ctx, X, (float *)ctx->d_work, E, M, N, st);
+  if (rc) return rc;
+  rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, eps, st);
   if (rc) return rc;
   uint16_t *x = X, *y = Y;
-  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, st);
+  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, st);
   if (rc) return rc;
   if (x != X)   // odd number of steps: result sits in Y, copy it home (muon_ns.py:274-276)
     ANC_CUDA(cudaMemcpyAsync(X, x, (size_t)E * M * N * 2, cudaMemcpyDeviceToDevice, st));

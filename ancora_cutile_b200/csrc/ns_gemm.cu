@@ -41,6 +41,7 @@ struct GemmParams {
   const uint16_t *D;      // axpy operand (modes 1, 2), same layout as C
   uint16_t *C;
   const uint32_t *tile_tab;
+  const float *mscale;    // per-matrix factor folded into the epilogue (nullable)
   uint32_t *status;
   int E, M, ldc;          // matrices, rows per matrix, row pitch of C/D in elements
   int tiles_per_matrix, total_tiles, kblocks, mode;
@@ -294,6 +295,12 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const size_t grow = (size_t)e * p.M + (size_t)i * BM + r;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+      // optional per-matrix factor r: mode 0 scales the product by r^2, mode 2 both terms by r
+      const bool scaled = p.mscale != nullptr && p.mode != 1;
+      const float sc = scaled ? p.mscale[e] : 1.f;
+      const float sc2 = __fmul_rn(sc, sc);
+      const float al = scaled ? __fmul_rn(p.alpha, sc) : p.alpha;
+      const float be = scaled ? __fmul_rn(p.beta, sc) : p.beta;
       for (int cc = 0; cc < 4 * w; ++cc) {
         uint32_t v[32];
         tc_ld32(taddr0 + cc * 32, v);
@@ -303,7 +310,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float f[32];
         if (p.mode == 0) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]);
+          for (int k = 0; k < 32; ++k)
+            f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k])) : __uint_as_float(v[k]);
         } else {
           const uint4 *drow = reinterpret_cast<const uint4 *>(p.D + grow * p.ldc + col);
 #pragma unroll
@@ -315,9 +323,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const float dlo = __uint_as_float(dw[k] << 16);
               const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
               f[k4 * 8 + 2 * k] =
-                  __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(p.alpha, dlo));
+                  __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(al, dlo));
               f[k4 * 8 + 2 * k + 1] =
-                  __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(p.alpha, dhi));
+                  __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
             }
           }
         }
@@ -604,6 +612,11 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after();
         const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
         uint8_t *my_row = epi_gen + r * 128;
+        const bool scaled = p.mscale != nullptr && p.mode != 1;
+        const float sc = scaled ? p.mscale[e] : 1.f;
+        const float sc2 = __fmul_rn(sc, sc);
+        const float al = scaled ? __fmul_rn(p.alpha, sc) : p.alpha;
+        const float be = scaled ? __fmul_rn(p.beta, sc) : p.beta;
         for (int cc = 0; cc < 4 * nblk; ++cc) {
           uint32_t v[32];
           tc_ld32(taddr0 + cc * 32, v);
@@ -618,7 +631,8 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             float f[8];
             if (p.mode == 0) {
 #pragma unroll
-              for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[k4 * 8 + k]);
+              for (int k = 0; k < 8; ++k)
+                f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k4 * 8 + k])) : __uint_as_float(v[k4 * 8 + k]);
             } else {
               const uint4 d = *slot;
               const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
@@ -626,9 +640,9 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int k = 0; k < 4; ++k) {
                 const float dlo = __uint_as_float(dw[k] << 16);
                 const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
-                f[2 * k] = __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(p.alpha, dlo));
+                f[2 * k] = __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(al, dlo));
                 f[2 * k + 1] =
-                    __fmaf_rn(p.beta, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(p.alpha, dhi));
+                    __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
               }
             }
 #pragma unroll
@@ -780,7 +794,8 @@ void anc_gemm_cache_destroy(anc_ctx *ctx) {
 }
 
 int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
-                       int E, int M, int N, float alpha, float beta, cudaStream_t st) {
+                       int E, int M, int N, float alpha, float beta, const float *mscale,
+                       cudaStream_t st) {
   ANC_REQUIRE(mode >= 0 && mode <= 2, "bad mode %d", mode);
   ANC_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0,
               "Newton-Schulz shape (%d x %d x %d) must be multiples of 128", E, M, N);
@@ -816,6 +831,7 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
   p.D = mode == 0 ? nullptr : (mode == 1 ? P : Q);
   p.C = C;
   p.tile_tab = tt.d_tab;
+  p.mscale = mscale;
   p.status = ctx->d_status;
   p.E = E;
   p.M = M;
@@ -865,5 +881,6 @@ extern "C" int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, cons
                                  void *stream) {
   ANC_REQUIRE(ctx && P && C, "NULL argument");
   anc_device_guard guard(ctx->device);
-  return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, anc_pick_stream(ctx, stream));
+  return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, nullptr,
+                            anc_pick_stream(ctx, stream));
 }

@@ -213,6 +213,30 @@ int anc_event_destroy(void *ev) {
   return ANC_OK;
 }
 
+int anc_stream_create(anc_ctx *ctx, void **stream) {
+  ANC_REQUIRE(ctx && stream, "NULL argument");
+  anc_device_guard g(ctx->device);
+  cudaStream_t st;
+  ANC_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  *stream = (void *)st;
+  return ANC_OK;
+}
+
+int anc_stream_destroy(anc_ctx *ctx, void *stream) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  if (!stream) return ANC_OK;
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  ANC_CUDA(cudaStreamDestroy((cudaStream_t)stream));
+  return ANC_OK;
+}
+
+int anc_stream_wait_event(void *stream, void *ev) {
+  ANC_REQUIRE(ev, "ev is NULL");
+  ANC_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0));
+  return ANC_OK;
+}
+
 __global__ void anc_flush_kernel(uint4 *p, size_t n16) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t stride = (size_t)gridDim.x * blockDim.x;

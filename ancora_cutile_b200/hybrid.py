@@ -81,6 +81,21 @@ class HybridOptimizer:
         e.ctx.sync(si)
         e.ctx.check_status()
 
+    def step_and_fetch(self, grads, stream_int=None):
+        """step() and the read-back of the updated bf16 weights as ONE pipelined call: the
+        gradient upload, the optimizer kernels and the download of finished parameters overlap
+        unit by unit.  Returns {name: uint16 bf16 bit patterns} (views of page-locked memory,
+        valid until the next call)."""
+        si = stream_int if stream_int is not None else self.si
+        bits, _, _ = self.engine.step_host(grads, si)
+        self.engine.ctx.check_status()
+        return bits
+
+    def pinned_grads(self):
+        """Page-locked numpy views, one per parameter, that ``step`` / ``step_and_fetch`` copy
+        from without an extra host copy when the caller writes gradients straight into them."""
+        return self.engine.pinned_grads()
+
     def weights(self):
         """bf16-valued fp32 weights for the next forward, per name."""
         return self.engine.weights()

@@ -9,25 +9,38 @@ Layout in HBM (all device buffers are single allocations; tensors are views):
                world * per_rank so the exchange is one in-place all-gather.
          p32, m, v : float32 arenas holding only this rank's slice [begin, end).
          g   : gradient arena, full size (each rank fills at least its slice).
-  Muon   p16 : bf16 arena ordered by owner rank, each rank's region padded to the largest.
-         p32, buf : float32 arenas of the owned matrices only.
-         g   : gradient arena over all matrices (each rank fills at least its own).
+  Muon   p16 : bf16 arena laid out [shape group][owner rank][matrix]; inside a group every
+               rank's region has the same (padded) size, so a group is gathered in place.
+         p32, buf : float32 arenas of the owned matrices only, [shape group][matrix].
+         g   : gradient arena with the p16 layout (each rank fills at least its own).
+
+The step is a sequence of UNITS -- the AdamW slice, then each Muon shape group (largest
+first) -- so that a unit's exchange (and, in ``step_host``, its host copies) overlaps the
+next unit's compute.
 """
+import ctypes as C
+
 import numpy as np
 
 from . import _lib as L
 from .adamw import ResidentAdamW, align_up
 from .bf16 import bits_to_f32, f32_to_bf16_bits
-from .buffers import DBuf, PinnedArray, get_context
+from .buffers import DBuf, Event, PinnedArray, get_context
 from .muon import MuonPlan, _UNSET, _schedule
-from .zero1 import greedy_partition, ns_cost, slice_bounds
+from .zero1 import ns_cost, partition_by_group, slice_bounds
+
+
+def _numel(shape):
+    return int(np.prod(shape, dtype=np.int64))
 
 
 class ResidentHybrid:
     def __init__(self, params, muon_names, no_decay_names=(), adamw_kw=None, muon_kw=None,
-                 grad_dtype="bf16", rounding="sr", seed=0, rank=0, world=1, comm=None,
+                 grad_dtype="bf16", rounding="sr", seed=0, rank=0, world=1, comm=None, p2p=None,
                  schedule=_UNSET, max_batch=0, ctx=None):
-        """params: {name: fp32 ndarray} (every rank passes the same dict)."""
+        """params: {name: fp32 ndarray} (every rank passes the same dict).
+        comm: zero1.Comm (NCCL all-gather after the step).  p2p: True to prepare the
+        copy-engine exchange (finish with ``connect_p2p``), which overlaps with compute."""
         self.ctx = ctx or get_context()
         self.rank, self.world, self.comm = int(rank), int(world), comm
         self.grad_dtype, self.rounding, self.seed = grad_dtype, rounding, int(seed)
@@ -45,15 +58,16 @@ class ResidentHybrid:
         self.shapes = {n: tuple(p.shape) for n, p in params.items()}
         nd = set(no_decay_names)
         c = self.ctx
+        W, R = self.world, self.rank
 
         # ---------------- AdamW arena
         self.a_off, off = {}, 0
         for n in self.adamw_names:
             self.a_off[n] = off
-            off = align_up(off + int(np.prod(self.shapes[n], dtype=np.int64)), 64)
+            off = align_up(off + _numel(self.shapes[n]), 64)
         self.a_total = off
-        self.a_per, self.a_padded = slice_bounds(max(off, 64), self.world, 64)
-        self.a_begin, self.a_end = self.rank * self.a_per, (self.rank + 1) * self.a_per
+        self.a_per, self.a_padded = slice_bounds(max(off, 64), W, 64)
+        self.a_begin, self.a_end = R * self.a_per, (R + 1) * self.a_per
         self.a_p16 = DBuf.zeros((self.a_padded,), np.uint16, c)
         self.a_g = DBuf.zeros((self.a_padded,), gdt, c)
         self.a_p32 = DBuf.zeros((self.a_per,), np.float32, c)
@@ -61,7 +75,7 @@ class ResidentHybrid:
         self.a_v = DBuf.zeros((self.a_per,), np.float32, c)
         tensors = []
         for n in self.adamw_names:
-            o, numel = self.a_off[n], int(np.prod(self.shapes[n], dtype=np.int64))
+            o, numel = self.a_off[n], _numel(self.shapes[n])
             flat = np.ascontiguousarray(params[n], dtype=np.float32).reshape(-1)
             self.a_p16.slice_elems(o, numel).upload(f32_to_bf16_bits(flat))
             lo, hi = max(o, self.a_begin), min(o + numel, self.a_end)
@@ -75,102 +89,181 @@ class ResidentHybrid:
                                 numel=numel, elem_offset=o,
                                 wd=0.0 if n in nd else self.adamw_kw["wd"]))
         self.adamw = ResidentAdamW(tensors, grad_dtype=grad_dtype, rounding=rounding, seed=seed, ctx=c)
-        if self.world > 1:
+        if W > 1:
             self.adamw.set_range(self.a_begin, self.a_end)
 
-        # ---------------- Muon arenas
-        costs = [ns_cost(*self.shapes[n]) for n in self.muon_names]
-        self.owner, self.load = greedy_partition(costs, self.world)
-        sizes = {n: int(np.prod(self.shapes[n], dtype=np.int64)) for n in self.muon_names}
-        region = [0] * self.world
-        self.m_off = {}                      # offset inside the owner's region
-        for n, r in zip(self.muon_names, self.owner):
-            self.m_off[n] = region[r]
-            region[r] += sizes[n]
-        self.m_per = align_up(max(region + [64]), 64)
-        self.m_p16 = DBuf.zeros((self.m_per * self.world,), np.uint16, c)
-        self.m_g = DBuf.zeros((self.m_per * self.world,), gdt, c)
-        mine = max(region[self.rank], 64)
-        self.m_p32 = DBuf.zeros((mine,), np.float32, c)
-        self.m_buf = DBuf.zeros((mine,), np.float32, c)
-        ws = []
+        # ---------------- Muon arenas: [group][owner][matrix]
+        mshapes = [self.shapes[n] for n in self.muon_names]
+        self.owner, self.load = partition_by_group(mshapes, W)
         self.m_owner = dict(zip(self.muon_names, self.owner))
+        gkeys = sorted({(min(s), max(s)) for s in mshapes})
+        self.groups = []                       # dicts: key, elems, per, base, names_by_rank, own_base
+        base = own = 0
+        self.m_off, self.m_own_off = {}, {}    # global arena offset / offset in the owned fp32 arenas
+        for key in gkeys:
+            e = key[0] * key[1]
+            by_rank = [[] for _ in range(W)]
+            for n, r in zip(self.muon_names, self.owner):
+                if (min(self.shapes[n]), max(self.shapes[n])) == key:
+                    by_rank[r].append(n)
+            per = max(len(x) for x in by_rank) * e
+            g = dict(key=key, elems=e, per=per, base=base, names=by_rank, own_base=own,
+                     total=sum(len(x) for x in by_rank) * e)
+            for r in range(W):
+                for k, n in enumerate(by_rank[r]):
+                    self.m_off[n] = base + r * per + k * e
+            for k, n in enumerate(by_rank[R]):
+                self.m_own_off[n] = own + k * e
+            base += W * per
+            own += len(by_rank[R]) * e
+            self.groups.append(g)
+        self.m_total = max(base, 64)
+        self.m_p16 = DBuf.zeros((self.m_total,), np.uint16, c)
+        self.m_g = DBuf.zeros((self.m_total,), gdt, c)
+        self.m_p32 = DBuf.zeros((max(own, 64),), np.float32, c)
+        self.m_buf = DBuf.zeros((max(own, 64),), np.float32, c)
+        self.m_owned_elems = own
+        ws = []
         for n in self.muon_names:
-            r, K, N = self.m_owner[n], *self.shapes[n]
-            g_off = r * self.m_per + self.m_off[n]
             w32 = np.ascontiguousarray(params[n], dtype=np.float32).reshape(-1)
-            self.m_p16.slice_elems(g_off, sizes[n]).upload(f32_to_bf16_bits(w32))
-            if r == self.rank:
-                self.m_p32.slice_elems(self.m_off[n], sizes[n]).upload(w32)
-                ws.append(dict(buf=self.m_buf.ptr + self.m_off[n] * 4, G=self.m_g.ptr + g_off * self._gdt.itemsize,
-                               p32=self.m_p32.ptr + self.m_off[n] * 4, p16=self.m_p16.ptr + g_off * 2,
-                               K=K, N=N))
+            self.m_p16.slice_elems(self.m_off[n], w32.size).upload(f32_to_bf16_bits(w32))
+            if self.m_owner[n] == R:
+                self.m_p32.slice_elems(self.m_own_off[n], w32.size).upload(w32)
+        for g in self.groups:                  # plan order = group order = arena order
+            for n in g["names"][R]:
+                K, N = self.shapes[n]
+                ws.append(dict(buf=self.m_buf.ptr + self.m_own_off[n] * 4,
+                               G=self.m_g.ptr + self.m_off[n] * self._gdt.itemsize,
+                               p32=self.m_p32.ptr + self.m_own_off[n] * 4,
+                               p16=self.m_p16.ptr + self.m_off[n] * 2, K=K, N=N))
         self.muon = MuonPlan(ws, grad_dtype=grad_dtype, max_batch=max_batch, ctx=c) if ws else None
+        # plan chunks per group (a group may be cut by max_batch)
+        self._chunks = {g["key"]: [] for g in self.groups}
+        if self.muon is not None:
+            for i in range(self.muon.num_chunks()):
+                _, _, M, Nn = self.muon.chunk_info(i)
+                self._chunks[(M, Nn)].append(i)
+        # units in execution order: AdamW, then groups by descending size (smallest last,
+        # because the last unit's exchange / copy-out is the one nothing overlaps)
+        self.units = ["adamw"] + [g["key"] for g in sorted(self.groups, key=lambda g: -g["total"])]
+        self._gmap = {g["key"]: g for g in self.groups}
         self._pin_g = None
         self._pin_w = None
+        self._streams = None
+        self.p2p = None
+        if p2p and W > 1:
+            from .zero1 import P2PExchange
+            self.p2p = P2PExchange(c, R, W, [self.a_p16.ptr, self.m_p16.ptr])
+
+    # ---------------------------------------------------------------- exchange set-up
+    def p2p_handles(self):
+        return self.p2p.local_handles()
+
+    def connect_p2p(self, all_handles):
+        self.p2p.connect(all_handles)
 
     # ---------------------------------------------------------------- locations
+    def _loc(self, name):
+        if name in self.a_off:
+            return self.a_p16, self.a_g, self.a_off[name]
+        return self.m_p16, self.m_g, self.m_off[name]
+
     def p16_view(self, name):
         """bf16 weight of ``name`` as a device view (what a forward pass would read)."""
-        n = int(np.prod(self.shapes[name], dtype=np.int64))
-        if name in self.a_off:
-            return self.a_p16.slice_elems(self.a_off[name], n, self.shapes[name])
-        return self.m_p16.slice_elems(self.m_owner[name] * self.m_per + self.m_off[name], n, self.shapes[name])
+        p16, _, o = self._loc(name)
+        return p16.slice_elems(o, _numel(self.shapes[name]), self.shapes[name])
 
     def grad_view(self, name):
-        n = int(np.prod(self.shapes[name], dtype=np.int64))
-        if name in self.a_off:
-            return self.a_g.slice_elems(self.a_off[name], n, self.shapes[name])
-        return self.m_g.slice_elems(self.m_owner[name] * self.m_per + self.m_off[name], n, self.shapes[name])
+        _, g, o = self._loc(name)
+        return g.slice_elems(o, _numel(self.shapes[name]), self.shapes[name])
 
     def owned_range(self, name):
         """(start, stop) flat element range of ``name`` whose state this rank holds."""
-        n = int(np.prod(self.shapes[name], dtype=np.int64))
+        n = _numel(self.shapes[name])
         if name in self.a_off:
             o = self.a_off[name]
             lo, hi = max(o, self.a_begin), min(o + n, self.a_end)
             return (lo - o, hi - o) if lo < hi else (0, 0)
         return (0, n) if self.m_owner[name] == self.rank else (0, 0)
 
+    def unit_ranges(self, unit):
+        """(arena index, own offset, own elems, whole offset, whole elems) of a unit in the
+        bf16 parameter / gradient arenas (arena 0 = AdamW, 1 = Muon)."""
+        if unit == "adamw":
+            return 0, self.a_begin, self.a_per, 0, self.a_padded
+        g = self._gmap[unit]
+        own = len(g["names"][self.rank]) * g["elems"]
+        return 1, g["base"] + self.rank * g["per"], own, g["base"], self.world * g["per"]
+
     # ---------------------------------------------------------------- the step
-    def step(self, si=None, exchange=True):
-        """One optimizer step on stream ``si``; asynchronous.  With world > 1 the updated
-        bf16 parameters are all-gathered at the end (``exchange``)."""
-        self.t += 1
+    def _compute_unit(self, unit, si):
         a, m = self.adamw_kw, self.muon_kw
-        if self.muon is not None:
-            self.muon.step(si, m["lr"], m["momentum"], m["nesterov"], m["ns_steps"], _schedule(self._sched))
-        self.adamw.step(si, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=self.t)
-        if exchange and self.world > 1:
+        if unit == "adamw":
+            tr = getattr(self, "trace_adamw", None)
+            if tr is not None:                 # benchmark hook: CUDA events around the launch
+                e0, e1 = Event(), Event()
+                e0.record(si)
+            self.adamw.step(si, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=self.t)
+            if tr is not None:
+                e1.record(si)
+                tr.append((e0, e1))
+        else:
+            for ci in self._chunks[unit]:
+                self.muon.step_chunk(ci, si, m["lr"], m["momentum"], m["nesterov"], m["ns_steps"],
+                                     _schedule(self._sched))
+
+    def _events(self, n):
+        if not hasattr(self, "_evpool"):
+            self._evpool = []
+        while len(self._evpool) < n:
+            self._evpool.append(Event())
+        return self._evpool[:n]
+
+    def step(self, si=None, exchange=True):
+        """One optimizer step on stream ``si``; asynchronous.  With world > 1 the updated bf16
+        parameters are exchanged: unit by unit over copy engines when the P2P exchange is
+        connected (overlapping the following units' compute), else by NCCL all-gathers."""
+        si = si or self.ctx.stream
+        self.t += 1
+        multi = exchange and self.world > 1
+        if multi and self.p2p is not None:
+            evs = self._events(len(self.units))
+            for u, ev in zip(self.units, evs):
+                self._compute_unit(u, si)
+                ev.record(si)
+                arena, off, n, _, _ = self.unit_ranges(u)
+                self.p2p.push(arena, off * 2, n * 2, ev)
+            self.p2p.finish(si)
+            return
+        for u in self.units:
+            self._compute_unit(u, si)
+        if multi:
             self.exchange(si)
 
     def exchange(self, si=None):
+        """NCCL path: one in-place all-gather per unit."""
         assert self.comm is not None, "world > 1 needs a communicator"
         self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, si)
-        self.comm.allgather_bf16(self.m_p16.ptr, self.m_per, si)
+        for g in self.groups:
+            self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], si)
 
     # ---------------------------------------------------------------- host traffic
     def pinned_grads(self):
         """Page-locked host staging for the gradients, one numpy view per name, laid out like
-        the device gradient arenas so that one copy per arena moves everything."""
+        the device gradient arenas so that one copy per unit moves everything."""
         if self._pin_g is None:
             pa = PinnedArray((self.a_padded,), self._gdt)
-            pm = PinnedArray((self.m_per * self.world,), self._gdt)
+            pm = PinnedArray((self.m_total,), self._gdt)
             views = {}
-            for n in self.adamw_names:
-                k = int(np.prod(self.shapes[n], dtype=np.int64))
-                views[n] = pa.array[self.a_off[n]:self.a_off[n] + k].reshape(self.shapes[n])
-            for n in self.muon_names:
-                k = int(np.prod(self.shapes[n], dtype=np.int64))
-                o = self.m_owner[n] * self.m_per + self.m_off[n]
-                views[n] = pm.array[o:o + k].reshape(self.shapes[n])
+            for n in self.adamw_names + self.muon_names:
+                src = pa if n in self.a_off else pm
+                o = self.a_off[n] if n in self.a_off else self.m_off[n]
+                views[n] = src.array[o:o + _numel(self.shapes[n])].reshape(self.shapes[n])
             self._pin_g = (pa, pm, views)
         return self._pin_g[2]
 
-    def upload_grads(self, grads, si=None):
-        """Host -> device copy of this rank's share of the gradients (asynchronous)."""
+    def _stage_grads(self, grads):
         views = self.pinned_grads()
-        pa, pm, _ = self._pin_g
         for n, v in views.items():
             g = grads[n]
             if isinstance(g, np.ndarray) and g.ctypes.data == v.ctypes.data and g.dtype == v.dtype:
@@ -178,36 +271,106 @@ class ResidentHybrid:
             if self._gdt == np.uint16 and np.asarray(g).dtype != np.uint16:
                 g = f32_to_bf16_bits(np.asarray(g, np.float32))
             np.copyto(v, np.asarray(g, dtype=self._gdt).reshape(v.shape))
+
+    def _h2d_unit(self, unit, stream):
+        pa, pm, _ = self._pin_g
+        arena, off, n, _, _ = self.unit_ranges(unit)
         it = self._gdt.itemsize
-        h2d = L.lib().anc_h2d
-        # AdamW: the owned slice; Muon: the owned region
-        L.check(h2d(self.ctx.handle, self.a_g.ptr + self.a_begin * it, pa.ptr + self.a_begin * it,
-                    self.a_per * it, si or None, 0))
-        L.check(h2d(self.ctx.handle, self.m_g.ptr + self.rank * self.m_per * it,
-                    pm.ptr + self.rank * self.m_per * it, self.m_per * it, si or None, 0))
-        return 2 * 0 + (self.a_per + self.m_per) * it
+        dev, host = (self.a_g, pa) if arena == 0 else (self.m_g, pm)
+        if n:
+            L.check(L.lib().anc_h2d(self.ctx.handle, dev.ptr + off * it, host.ptr + off * it, n * it,
+                                    stream or None, 0))
+        return n * it
+
+    def _d2h_unit(self, unit, stream):
+        wa, wm = self._pin_w
+        arena, off, n, _, _ = self.unit_ranges(unit)
+        dev, host = (self.a_p16, wa) if arena == 0 else (self.m_p16, wm)
+        if n:
+            L.check(L.lib().anc_d2h(self.ctx.handle, host.ptr + off * 2, dev.ptr + off * 2, n * 2,
+                                    stream or None, 0))
+        return n * 2
+
+    def upload_grads(self, grads, si=None):
+        """Host -> device copy of this rank's share of the gradients (asynchronous)."""
+        self._stage_grads(grads)
+        return sum(self._h2d_unit(u, si) for u in self.units)
+
+    def _ensure_host_side(self):
+        if self._pin_w is None:
+            self._pin_w = (PinnedArray((self.a_padded,), np.uint16), PinnedArray((self.m_total,), np.uint16))
+        if self._streams is None:
+            ss = []
+            for _ in range(2):
+                s = C.c_void_p()
+                L.check(L.lib().anc_stream_create(self.ctx.handle, C.byref(s)))
+                ss.append(s.value)
+            self._streams = ss
+        self.pinned_grads()
+
+    def _weight_views(self):
+        wa, wm = self._pin_w
+        out = {}
+        for n in self.adamw_names + self.muon_names:
+            src = wa if n in self.a_off else wm
+            o = self.a_off[n] if n in self.a_off else self.m_off[n]
+            out[n] = src.array[o:o + _numel(self.shapes[n])].reshape(self.shapes[n])
+        return out
+
+    def step_host(self, grads, si=None):
+        """The whole round trip a host-API caller makes, pipelined unit by unit on three
+        streams: gradients host -> device, the step (and, with world > 1, the exchange), this
+        rank's updated bf16 parameters device -> host.  Returns ({name: uint16 view of
+        page-locked memory}, bytes copied in, bytes copied out) after synchronising.
+        With world > 1 only the parameters this rank owns are copied out."""
+        si = si or self.ctx.stream
+        self._ensure_host_side()
+        self._stage_grads(grads)
+        s_in, s_out = self._streams
+        self.t += 1
+        nu = len(self.units)
+        evs = self._events(3 * nu + 1)
+        ev_in, ev_c, ev_out = evs[:nu], evs[nu:2 * nu], evs[2 * nu:3 * nu]
+        start = evs[3 * nu]
+        start.record(si)                       # copies may not overtake work queued earlier on si
+        lib = L.lib()
+        L.check(lib.anc_stream_wait_event(s_in, start.handle))
+        L.check(lib.anc_stream_wait_event(s_out, start.handle))
+        h2d = d2h = 0
+        multi = self.world > 1
+        for k, u in enumerate(self.units):
+            h2d += self._h2d_unit(u, s_in)
+            ev_in[k].record(s_in)
+            L.check(lib.anc_stream_wait_event(si, ev_in[k].handle))
+            self._compute_unit(u, si)
+            ev_c[k].record(si)
+            if multi and self.p2p is not None:
+                arena, off, n, _, _ = self.unit_ranges(u)
+                self.p2p.push(arena, off * 2, n * 2, ev_c[k])
+            L.check(lib.anc_stream_wait_event(s_out, ev_c[k].handle))
+            d2h += self._d2h_unit(u, s_out)
+            ev_out[k].record(s_out)
+        if multi:
+            if self.p2p is not None:
+                self.p2p.finish(si)
+            else:
+                self.exchange(si)
+        for k in range(nu):
+            L.check(lib.anc_stream_wait_event(si, ev_out[k].handle))
+        self.ctx.sync(si)
+        return self._weight_views(), h2d, d2h
 
     def download_weights_bits(self, si=None, sync=True):
         """Device -> host copy of every bf16 parameter into page-locked memory; returns
         ({name: uint16 view}, bytes copied)."""
-        if self._pin_w is None:
-            self._pin_w = (PinnedArray((self.a_padded,), np.uint16),
-                           PinnedArray((self.m_per * self.world,), np.uint16))
+        self._ensure_host_side()
         wa, wm = self._pin_w
         d2h = L.lib().anc_d2h
         L.check(d2h(self.ctx.handle, wa.ptr, self.a_p16.ptr, self.a_padded * 2, si or None, 0))
-        L.check(d2h(self.ctx.handle, wm.ptr, self.m_p16.ptr, self.m_per * self.world * 2, si or None, 0))
+        L.check(d2h(self.ctx.handle, wm.ptr, self.m_p16.ptr, self.m_total * 2, si or None, 0))
         if sync:
             self.ctx.sync(si)
-        out = {}
-        for n in self.adamw_names:
-            k = int(np.prod(self.shapes[n], dtype=np.int64))
-            out[n] = wa.array[self.a_off[n]:self.a_off[n] + k].reshape(self.shapes[n])
-        for n in self.muon_names:
-            k = int(np.prod(self.shapes[n], dtype=np.int64))
-            o = self.m_owner[n] * self.m_per + self.m_off[n]
-            out[n] = wm.array[o:o + k].reshape(self.shapes[n])
-        return out, (self.a_padded + self.m_per * self.world) * 2
+        return self._weight_views(), (self.a_padded + self.m_total) * 2
 
     def weights(self):
         bits, _ = self.download_weights_bits()
@@ -227,8 +390,8 @@ class ResidentHybrid:
             m32 = self.m_p32.to_numpy()
             for n in self.muon_names:
                 if self.m_owner[n] == self.rank:
-                    k = int(np.prod(self.shapes[n], dtype=np.int64))
-                    out[n] = (0, k, m32[self.m_off[n]:self.m_off[n] + k].copy())
+                    k = _numel(self.shapes[n])
+                    out[n] = (0, k, m32[self.m_own_off[n]:self.m_own_off[n] + k].copy())
         return out
 
     def state_bytes(self):
@@ -236,6 +399,10 @@ class ResidentHybrid:
                                       self.m_p16, self.m_g, self.m_p32, self.m_buf))
 
     def free(self):
+        self.ctx.sync()
+        if self.p2p is not None:
+            self.p2p.destroy()
+            self.p2p = None
         self.adamw.free()
         if self.muon is not None:
             self.muon.free()
@@ -247,3 +414,10 @@ class ResidentHybrid:
             for p in grp:
                 p.free()
         self._pin_g = self._pin_w = None
+        if self._streams:
+            for s in self._streams:
+                L.lib().anc_stream_destroy(self.ctx.handle, s)
+            self._streams = None
+        for e in getattr(self, "_evpool", []):
+            e.destroy()
+        self._evpool = []

@@ -206,9 +206,19 @@ def main():
         import torch
         import torch.distributed as dist
         dist.init_process_group("gloo", rank=rank, world_size=world)
-        box = [nccl_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        comm = Comm(ctx, box[0], rank, world)
+        # NCCL may print its version banner on stdout; keep stdout for the one JSON line
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            box = [nccl_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            comm = Comm(ctx, box[0], rank, world)
+            comm.barrier(ctx.stream)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     def barrier():
         ctx.sync()
@@ -226,10 +236,17 @@ def main():
     anc.set_polar_express(True)
     params = S.synthetic_params(shp, seed=0)
     no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
+    use_p2p = world > 1 and os.environ.get("ANCORA_EXCHANGE", "p2p") == "p2p"
     eng = anc.ResidentHybrid(params, muon_names, no_decay_names=no_decay, adamw_kw=ADAMW_KW, muon_kw=MUON_KW,
                              grad_dtype="bf16", rounding="sr", seed=SEED_SR, rank=rank, world=world,
-                             comm=comm, ctx=ctx)
+                             comm=comm, p2p=use_p2p, schedule=anc.PE_SCHEDULE, ctx=ctx)
     del params
+    if use_p2p:
+        box = [None] * world
+        dist.all_gather_object(box, eng.p2p_handles())
+        eng.connect_p2p(box)
+    config["exchange"] = ("copy-engine pushes over NVLink (IPC), overlapped per unit" if use_p2p
+                          else ("NCCL all-gather" if world > 1 else "none"))
     # synthetic bf16 gradients, written into the page-locked staging views and uploaded once
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)
@@ -249,7 +266,6 @@ def main():
     if eng.muon is not None:
         eng.muon.set_timing(True)
     e0, e1 = anc.Event(), anc.Event()
-    ea = [(anc.Event(), anc.Event()) for _ in range(args.steps)]
 
     for _ in range(args.warmup):
         eng.step(ctx.stream)
@@ -261,23 +277,15 @@ def main():
     ns_ms = mom_ms = upd_ms = nrm_ms = adamw_ms = 0.0
     ns_flops = 0.0
     gemm_launches = 0
+    eng.trace_adamw = []                # CUDA events around each AdamW launch (no synchronisation)
     barrier()
     e0.record(ctx.stream)
     for k in range(args.steps):
-        # the step, with the AdamW launch bracketed by events (events do not synchronise)
-        ea0, ea1 = ea[k]
-        eng.t += 1
-        a, m = eng.adamw_kw, eng.muon_kw
-        if eng.muon is not None:
-            eng.muon.step(ctx.stream, m["lr"], m["momentum"], m["nesterov"], m["ns_steps"], anc.PE_SCHEDULE)
-        ea0.record(ctx.stream)
-        eng.adamw.step(ctx.stream, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=eng.t)
-        ea1.record(ctx.stream)
-        if world > 1:
-            eng.exchange(ctx.stream)
+        eng.step(ctx.stream)            # with N > 1 this includes the exchange of the bf16 parameters
     e1.record(ctx.stream)
     barrier()
-    adamw_ms = sum(a0.elapsed_ms(a1) for a0, a1 in ea)
+    adamw_ms = sum(a0.elapsed_ms(a1) for a0, a1 in eng.trace_adamw)
+    eng.trace_adamw = None
     if eng.muon is not None:
         t = eng.muon.last_timing()      # per-phase spans accumulated over the K timed steps
         ns_ms, mom_ms, upd_ms, nrm_ms = t["ns_ms"], t["momentum_ms"], t["update_ms"], t["normalize_ms"]
@@ -291,15 +299,15 @@ def main():
     ns_tflops = ns_flops / (ns_ms * 1e-3) / 1e12 if ns_ms > 0 else 0.0
     a_owned = min(eng.a_total, eng.a_end) - min(eng.a_total, eng.a_begin)
     adamw_gbs = 28.0 * a_owned / (adamw_ms / K * 1e-3) / 1e9 if adamw_ms > 0 else 0.0
-    m_owned = eng.m_p32.shape[0] if eng.muon is not None else 0
+    m_owned = eng.m_owned_elems
     elem_gbs = 24.0 * m_owned / ((mom_ms + upd_ms) / K * 1e-3) / 1e9 if (mom_ms + upd_ms) > 0 else 0.0
-    n_groups = len({(min(shp[n]), max(shp[n])) for n in muon_names})
+    n_groups = len(eng.groups)
     out = {
         "metric": "hybrid_optimizer_step_params_per_s", "value": value, "unit": "params/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": config,
-        "roofline": {"bound": "tensor", "kernel": "ns_gemm_kernel", "achieved": ns_tflops,
+        "roofline": {"bound": "tensor", "kernel": "ns_gemm_pair_kernel", "achieved": ns_tflops,
                      "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": ns_tflops / peaks["bf16_tflops_sustained"], "traffic": None,
                      "peak_kind": f"{peaks['src']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
@@ -312,27 +320,29 @@ def main():
                              "frac": elem_gbs / peaks["hbm_gbs"], "bytes_per_param": 24,
                              "momentum_ms": mom_ms / K, "update_ms": upd_ms / K, "normalize_ms": nrm_ms / K},
         "clocks": clocks,
-        "gpu_launches": (gemm_launches // K) + 4 * n_groups + 1,
+        # per step: 3 GEMM launches per iteration and group, momentum + finalize + update per group, AdamW
+        "gpu_launches": (gemm_launches // K) + 3 * n_groups + 1,
         "state_bytes_per_gpu": eng.state_bytes() + (eng.muon.scratch_bytes() if eng.muon else 0),
     }
 
-    # ---- end-to-end: host gradients in, bf16 weights out, through the public class ----
+    # ---- end-to-end: host gradients in, bf16 weights out, through the public call path ----
     if not args.no_e2e:
         h2d = d2h = 0
         for _ in range(2):
-            eng.upload_grads(pin, ctx.stream); eng.step(ctx.stream); eng.download_weights_bits(ctx.stream)
+            eng.step_host(pin, ctx.stream)
         barrier()
+        t0 = time.perf_counter()
         e0.record(ctx.stream)
         for _ in range(args.steps):
-            h2d = eng.upload_grads(pin, ctx.stream)
-            eng.step(ctx.stream)
-            _, d2h = eng.download_weights_bits(ctx.stream, sync=True)
+            _, h2d, d2h = eng.step_host(pin, ctx.stream)     # synchronises: the result is on the host
         e1.record(ctx.stream)
         barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_ms(e1)) / args.steps
+        wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        e2e_ms = max_over_ranks(max(e0.elapsed_ms(e1) / args.steps, wall_ms))
         out["e2e"] = {"value": total_params / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                      "api": "ResidentHybrid.upload_grads + step + download_weights_bits (the calls HybridOptimizer.step/weights make)"}
+                      "api": "HybridOptimizer.step_and_fetch -> ResidentHybrid.step_host: page-locked bf16 "
+                             "gradients in, updated bf16 parameters out, pipelined per unit on 3 streams"}
     status = ctx.status()
     out["device_status"] = status
 

@@ -88,6 +88,10 @@ ANC_API int anc_event_record(void *ev, void *stream);
 ANC_API int anc_event_sync(void *ev);
 ANC_API int anc_event_elapsed_ms(void *start, void *stop, float *ms);
 ANC_API int anc_event_destroy(void *ev);
+/* Extra streams for overlapping copies / collectives with compute. */
+ANC_API int anc_stream_create(anc_ctx *ctx, void **stream);
+ANC_API int anc_stream_destroy(anc_ctx *ctx, void *stream);
+ANC_API int anc_stream_wait_event(void *stream, void *ev);
 
 /* Writes `bytes` of device memory (larger than L2) to evict cached lines between
  * timed iterations. */
@@ -166,6 +170,17 @@ ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, i
  * rounding (muon.py:176,200). */
 ANC_API int anc_muon_step(anc_muon_plan *plan, double lr, float momentum, int nesterov, int ns_steps,
                           const float *coeffs, float eps, void *stream);
+/* The step is a sequence of chunks (one shape group, at most max_batch matrices) that run
+ * one after another through the shared scratch.  These calls expose the chunks so a caller
+ * can overlap each chunk's input copy / output copy / exchange with the next chunk's
+ * compute using its own streams and events.  info = {index of the chunk's first weight among
+ * the weights this plan steps (registration order), matrix count, M, N}.  Chunks must be
+ * issued on ONE stream in any order that covers each exactly once per step. */
+ANC_API int anc_muon_plan_num_chunks(anc_muon_plan *plan, int *n);
+ANC_API int anc_muon_plan_chunk_info(anc_muon_plan *plan, int chunk, int32_t info[4]);
+ANC_API int anc_muon_step_chunk(anc_muon_plan *plan, int chunk, double lr, float momentum,
+                                int nesterov, int ns_steps, const float *coeffs, float eps,
+                                void *stream);
 /* Per-phase device time accumulated over every anc_muon_step since the previous call
  * (timing enabled with anc_muon_plan_set_timing(plan, 1); CUDA events on the step's
  * stream, no synchronisation inside the step): ms spent in momentum, normalise,
@@ -255,6 +270,19 @@ ANC_API int anc_comm_allgather_bf16(anc_comm *comm, uint16_t *arena, uint64_t el
 ANC_API int anc_comm_bcast_segments(anc_comm *comm, uint16_t *const *ptr, const uint64_t *elems,
                                     const int *root, int n_segments, void *stream);
 ANC_API int anc_comm_barrier(anc_comm *comm, void *stream);
+
+/* Copy-engine exchange over NVLink (no counterpart in the reference).  A rank exports its
+ * arena (cudaMalloc'ed) as a 64-byte IPC handle; peers open it and push their slices into
+ * it with anc_d2d on their own streams, then raise the receiver's flag with anc_p2p_signal
+ * on the same stream.  anc_p2p_wait_flags launches a bounded wait for flags[i] >= value for
+ * all i != skip (a wait that runs out sets status bit 0x10 and returns). */
+#define ANC_IPC_HANDLE_BYTES 64
+ANC_API int anc_ipc_export_mem(anc_ctx *ctx, void *dptr, void *handle64);
+ANC_API int anc_ipc_open_mem(anc_ctx *ctx, const void *handle64, void **peer_ptr);
+ANC_API int anc_ipc_close_mem(anc_ctx *ctx, void *peer_ptr);
+ANC_API int anc_p2p_signal(anc_ctx *ctx, uint32_t *remote_flag, uint32_t value, void *stream);
+ANC_API int anc_p2p_wait_flags(anc_ctx *ctx, const uint32_t *flags, int n, int skip, uint32_t value,
+                               void *stream);
 
 #ifdef __cplusplus
 }
