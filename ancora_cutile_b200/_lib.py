@@ -74,9 +74,9 @@ SIGNATURES = {
     "anc_adamw_plan_destroy": (_i, [_vp]),
     "anc_muon_plan_create": (_i, [_vp, C.POINTER(MuonWeight), _i, _i, _i, _i, _pp]),
     "anc_muon_step": (_i, [_vp, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
-    "anc_muon_plan_num_chunks": (_i, [_vp, C.POINTER(_i)]),
-    "anc_muon_plan_chunk_info": (_i, [_vp, _i, C.POINTER(C.c_int32)]),
-    "anc_muon_step_chunk": (_i, [_vp, _i, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
+    "anc_muon_plan_num_groups": (_i, [_vp, C.POINTER(_i)]),
+    "anc_muon_plan_group_info": (_i, [_vp, _i, C.POINTER(C.c_int32)]),
+    "anc_muon_step_range": (_i, [_vp, _i, _i, _i, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
     "anc_muon_plan_set_timing": (_i, [_vp, _i]),
     "anc_muon_plan_last_timing": (_i, [_vp, C.POINTER(_f), C.POINTER(_d), C.POINTER(_i)]),
     "anc_muon_plan_scratch_bytes": (_i, [_vp, C.POINTER(_u64)]),

@@ -20,8 +20,8 @@ struct anc_ctx {
 };
 
 // entries of the device tables the Muon plan builds for the group launches
-struct anc_mom_entry { float *buf; const void *g; int slot, K, N, tr; };
-struct anc_upd_entry { float *p32; uint16_t *p16; int slot, K, N, tr; };
+struct anc_mom_entry { float *buf; const void *g; int K, N, tr, _pad; };
+struct anc_upd_entry { float *p32; uint16_t *p16; int K, N, tr, _pad; };
 
 // device status bits
 #define ANC_DEV_TIMEOUT_TMA 0x1u     // producer/consumer mbarrier wait ran out

@@ -18,18 +18,18 @@ constexpr int kTile = 64;
 constexpr int kThreads = 256;
 constexpr int kPad = 8;   // row pitch 72 bf16 = 144 B: 16-byte aligned rows, few bank conflicts
 
-// Table entries.  `slot` selects the weight's matrix inside the packed Newton-Schulz
+// Table entries.  The i-th entry of a launched range uses slot i of the packed Newton-Schulz
 // operand: slot s starts at element s * K * N and holds (K,N) if !tr, else (N,K).
 struct MomW {
   float *buf;
   const void *g;
-  int slot, K, N, tr;
+  int K, N, tr, _pad;
 };
 
 struct UpdW {
   float *p32;
   uint16_t *p16;
-  int slot, K, N, tr;
+  int K, N, tr, _pad;
 };
 
 __device__ __forceinline__ uint32_t rne16(float x) {
@@ -41,9 +41,9 @@ __device__ __forceinline__ float bf16_f32(uint32_t h) { return __uint_as_float(h
 // 128-bit accesses.  Returns this thread's sum of squares of the bf16-rounded u values
 // (added in element order: first row left to right, then the second row).
 template <bool kGradF32>
-__device__ __forceinline__ float momentum_tile(const MomW &w, uint16_t *xbase, int ti, int tj, float mu,
-                                               int nesterov, uint16_t (*sm)[kTile + kPad]) {
-  uint16_t *wx = xbase + (size_t)w.slot * w.K * w.N;
+__device__ __forceinline__ float momentum_tile(const MomW &w, int slot, uint16_t *xbase, int ti, int tj,
+                                               float mu, int nesterov, uint16_t (*sm)[kTile + kPad]) {
+  uint16_t *wx = xbase + (size_t)slot * w.K * w.N;
   const int c8 = (threadIdx.x & 7) * 8;
   const int r0 = threadIdx.x >> 3;
   const int col = tj * kTile + c8;
@@ -107,9 +107,9 @@ __device__ __forceinline__ float momentum_tile(const MomW &w, uint16_t *xbase, i
   return ss;
 }
 
-__device__ __forceinline__ void update_tile(const UpdW &w, const uint16_t *obase, float lr_scale,
+__device__ __forceinline__ void update_tile(const UpdW &w, int slot, const uint16_t *obase, float lr_scale,
                                             int ti, int tj, uint16_t (*sm)[kTile + kPad]) {
-  const uint16_t *wo = obase + (size_t)w.slot * w.K * w.N;
+  const uint16_t *wo = obase + (size_t)slot * w.K * w.N;
   const int c8 = (threadIdx.x & 7) * 8;
   const int r0 = threadIdx.x >> 3;
   const int col = tj * kTile + c8;
@@ -196,8 +196,8 @@ momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int ti
     const int t = b - wi * tiles_per_w;
     const MomW w = table[wi];
     const int tn = w.N / kTile;
-    const float ss = momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
-    if (partial) tile_sumsq_store(ss, partial + (size_t)w.slot * tiles_per_w + t, wsum);
+    const float ss = momentum_tile<kGradF32>(w, wi, xbase, t / tn, t % tn, mu, nesterov, sm);
+    if (partial) tile_sumsq_store(ss, partial + (size_t)wi * tiles_per_w + t, wsum);
   }
 }
 
@@ -233,7 +233,7 @@ update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, in
     const int t = b - wi * tiles_per_w;
     const UpdW w = table[wi];
     const int tn = w.N / kTile;
-    update_tile(w, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm);
+    update_tile(w, wi, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm);
   }
 }
 
@@ -245,7 +245,7 @@ momentum_one_kernel(MomW w, uint16_t *xbase, float mu, int nesterov) {
   const int tn = w.N / kTile;
   const int total = (w.K / kTile) * tn;
   for (int t = blockIdx.x; t < total; t += gridDim.x)
-    (void)momentum_tile<kGradF32>(w, xbase, t / tn, t % tn, mu, nesterov, sm);
+    (void)momentum_tile<kGradF32>(w, 0, xbase, t / tn, t % tn, mu, nesterov, sm);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -254,7 +254,7 @@ update_one_kernel(UpdW w, const uint16_t *obase, float lr_scale) {
   const int tn = w.N / kTile;
   const int total = (w.K / kTile) * tn;
   for (int t = blockIdx.x; t < total; t += gridDim.x)
-    update_tile(w, obase, lr_scale, t / tn, t % tn, sm);
+    update_tile(w, 0, obase, lr_scale, t / tn, t % tn, sm);
 }
 
 // ---- Frobenius normalisation ------------------------------------------------
@@ -352,7 +352,7 @@ int anc_launch_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype,
                         int N, float momentum, int nesterov, int transposed, cudaStream_t st) {
   int rc = check_shape(K, N);
   if (rc) return rc;
-  MomW w = {buf, g, 0, K, N, transposed ? 1 : 0};
+  MomW w = {buf, g, K, N, transposed ? 1 : 0, 0};
   int tiles = (K / kTile) * (N / kTile);
   int grid = tiles < ctx->sm_count * 8 ? tiles : ctx->sm_count * 8;
   if (grad_dtype == ANC_GRAD_F32)
@@ -367,7 +367,7 @@ int anc_launch_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O
                       float lr_scale, int transposed, cudaStream_t st) {
   int rc = check_shape(K, N);
   if (rc) return rc;
-  UpdW w = {p32, p16, 0, K, N, transposed ? 1 : 0};
+  UpdW w = {p32, p16, K, N, transposed ? 1 : 0, 0};
   int tiles = (K / kTile) * (N / kTile);
   int grid = tiles < ctx->sm_count * 8 ? tiles : ctx->sm_count * 8;
   update_one_kernel<<<grid, kThreads, 0, st>>>(w, O, lr_scale);

@@ -131,9 +131,8 @@ int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_wei
     std::vector<anc_upd_entry> upd;
     for (size_t s = 0; s < g.widx.size(); ++s) {
       const anc_muon_weight &w = pl->weights[g.widx[s]];
-      const int slot = (int)(s % E);
-      mom.push_back({w.buf, w.g, slot, w.K, w.N, w.K > w.N ? 1 : 0});
-      upd.push_back({w.p32, w.p16, slot, w.K, w.N, w.K > w.N ? 1 : 0});
+      mom.push_back({w.buf, w.g, w.K, w.N, w.K > w.N ? 1 : 0, 0});
+      upd.push_back({w.p32, w.p16, w.K, w.N, w.K > w.N ? 1 : 0, 0});
     }
     cudaError_t e = cudaMalloc((void **)&g.d_mom, mom.size() * sizeof(anc_mom_entry));
     if (e == cudaSuccess) e = cudaMalloc((void **)&g.d_upd, upd.size() * sizeof(anc_upd_entry));
@@ -248,32 +247,36 @@ int anc_muon_step(anc_muon_plan *pl, double lr, float momentum, int nesterov, in
   return ANC_OK;
 }
 
-int anc_muon_plan_num_chunks(anc_muon_plan *pl, int *n) {
+int anc_muon_plan_num_groups(anc_muon_plan *pl, int *n) {
   ANC_REQUIRE(pl && n, "NULL argument");
-  *n = (int)plan_chunks(pl).size();
+  *n = (int)pl->groups.size();
   return ANC_OK;
 }
 
-int anc_muon_plan_chunk_info(anc_muon_plan *pl, int chunk, int32_t info[4]) {
+int anc_muon_plan_group_info(anc_muon_plan *pl, int group, int32_t info[4]) {
   ANC_REQUIRE(pl && info, "NULL argument");
-  std::vector<ChunkRef> cs = plan_chunks(pl);
-  ANC_REQUIRE(chunk >= 0 && chunk < (int)cs.size(), "chunk %d out of range", chunk);
-  const Group &g = pl->groups[cs[chunk].group];
-  info[0] = g.widx[cs[chunk].w0];   // index (among this plan's weights, in registration order)
-  info[1] = cs[chunk].count;
+  ANC_REQUIRE(group >= 0 && group < (int)pl->groups.size(), "group %d out of range", group);
+  const Group &g = pl->groups[group];
+  info[0] = (int)g.widx.size();
+  info[1] = pl->max_batch > 0 ? std::min(pl->max_batch, (int)g.widx.size()) : (int)g.widx.size();
   info[2] = g.M;
   info[3] = g.Nn;
   return ANC_OK;
 }
 
-int anc_muon_step_chunk(anc_muon_plan *pl, int chunk, double lr, float momentum, int nesterov,
-                        int ns_steps, const float *coeffs, float eps, void *stream) {
+int anc_muon_step_range(anc_muon_plan *pl, int group, int first, int count, double lr, float momentum,
+                        int nesterov, int ns_steps, const float *coeffs, float eps, void *stream) {
   ANC_REQUIRE(pl && (coeffs || ns_steps == 0), "NULL argument");
   ANC_REQUIRE(ns_steps >= 0 && ns_steps <= 64, "bad ns_steps %d", ns_steps);
-  std::vector<ChunkRef> cs = plan_chunks(pl);
-  ANC_REQUIRE(chunk >= 0 && chunk < (int)cs.size(), "chunk %d out of range", chunk);
+  ANC_REQUIRE(group >= 0 && group < (int)pl->groups.size(), "group %d out of range", group);
+  const int total = (int)pl->groups[group].widx.size();
+  const int cap = pl->max_batch > 0 ? std::min(pl->max_batch, total) : total;
+  ANC_REQUIRE(first >= 0 && count > 0 && first + count <= total, "range [%d,+%d) outside the group's %d weights",
+              first, count, total);
+  ANC_REQUIRE(count <= cap, "range of %d matrices exceeds the scratch batch of %d", count, cap);
   anc_device_guard guard(pl->ctx->device);
-  return step_chunk(pl, cs[chunk], lr, momentum, nesterov, ns_steps, coeffs, eps,
+  ChunkRef c = {group, first, count};
+  return step_chunk(pl, c, lr, momentum, nesterov, ns_steps, coeffs, eps,
                     anc_pick_stream(pl->ctx, stream));
 }
 

@@ -49,23 +49,23 @@ class MuonPlan:
         L.check(L.lib().anc_muon_step(self.handle, float(lr), float(momentum), int(bool(nesterov)),
                                       int(ns_steps), flat, float(eps), C.c_void_p(si or None)))
 
-    def num_chunks(self):
+    def num_groups(self):
         n = C.c_int()
-        L.check(L.lib().anc_muon_plan_num_chunks(self.handle, C.byref(n)))
+        L.check(L.lib().anc_muon_plan_num_groups(self.handle, C.byref(n)))
         return n.value
 
-    def chunk_info(self, i):
-        """(first weight index among this plan's weights, matrix count, M, N) of chunk i."""
+    def group_info(self, g):
+        """(weights in the group, largest range the scratch holds, M, N)."""
         info = (C.c_int32 * 4)()
-        L.check(L.lib().anc_muon_plan_chunk_info(self.handle, int(i), info))
+        L.check(L.lib().anc_muon_plan_group_info(self.handle, int(g), info))
         return tuple(info)
 
-    def step_chunk(self, i, si, lr, momentum, nesterov, ns_steps, schedule, eps=1e-7):
+    def step_range(self, g, first, count, si, lr, momentum, nesterov, ns_steps, schedule, eps=1e-7):
         co = muon_ns.coeff_list(schedule, ns_steps)
         flat = (C.c_float * max(3 * ns_steps, 1))(*[float(x) for t in co for x in t])
-        L.check(L.lib().anc_muon_step_chunk(self.handle, int(i), float(lr), float(momentum),
-                                            int(bool(nesterov)), int(ns_steps), flat, float(eps),
-                                            C.c_void_p(si or None)))
+        L.check(L.lib().anc_muon_step_range(self.handle, int(g), int(first), int(count), float(lr),
+                                            float(momentum), int(bool(nesterov)), int(ns_steps), flat,
+                                            float(eps), C.c_void_p(si or None)))
 
     def set_timing(self, on):
         L.check(L.lib().anc_muon_plan_set_timing(self.handle, int(bool(on))))

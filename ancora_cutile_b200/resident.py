@@ -88,6 +88,7 @@ class ResidentHybrid:
                                 m=self.a_m.ptr + rel, v=self.a_v.ptr + rel, p16=self.a_p16.ptr + o * 2,
                                 numel=numel, elem_offset=o,
                                 wd=0.0 if n in nd else self.adamw_kw["wd"]))
+        self._adamw_tensors = tensors
         self.adamw = ResidentAdamW(tensors, grad_dtype=grad_dtype, rounding=rounding, seed=seed, ctx=c)
         if W > 1:
             self.adamw.set_range(self.a_begin, self.a_end)
@@ -137,16 +138,19 @@ class ResidentHybrid:
                                p32=self.m_p32.ptr + self.m_own_off[n] * 4,
                                p16=self.m_p16.ptr + self.m_off[n] * 2, K=K, N=N))
         self.muon = MuonPlan(ws, grad_dtype=grad_dtype, max_batch=max_batch, ctx=c) if ws else None
-        # plan chunks per group (a group may be cut by max_batch)
-        self._chunks = {g["key"]: [] for g in self.groups}
-        if self.muon is not None:
-            for i in range(self.muon.num_chunks()):
-                _, _, M, Nn = self.muon.chunk_info(i)
-                self._chunks[(M, Nn)].append(i)
-        # units in execution order: AdamW, then groups by descending size (smallest last,
-        # because the last unit's exchange / copy-out is the one nothing overlaps)
-        self.units = ["adamw"] + [g["key"] for g in sorted(self.groups, key=lambda g: -g["total"])]
+        # Units of work, each a contiguous span of this rank's share of an arena:
+        #   ("adamw", plan, begin, end)            arena-0 elements [begin, end)
+        #   ("muon", plan group, first, count)     matrices [first, first+count) of a shape group
         self._gmap = {g["key"]: g for g in self.groups}
+        self._pgroup = {}                      # shape key -> (plan group index, scratch batch)
+        if self.muon is not None:
+            for gi in range(self.muon.num_groups()):
+                _, cap, M, Nn = self.muon.group_info(gi)
+                self._pgroup[(M, Nn)] = (gi, cap)
+        self.host_chunk_elems = 64 << 20       # step_host cuts units to <= 128 MiB of bf16
+        self._sub_plans = []
+        self.units = self._make_units(None)
+        self._host_units = None
         self._pin_g = None
         self._pin_w = None
         self._streams = None
@@ -186,31 +190,56 @@ class ResidentHybrid:
             return (lo - o, hi - o) if lo < hi else (0, 0)
         return (0, n) if self.m_owner[name] == self.rank else (0, 0)
 
-    def unit_ranges(self, unit):
-        """(arena index, own offset, own elems, whole offset, whole elems) of a unit in the
-        bf16 parameter / gradient arenas (arena 0 = AdamW, 1 = Muon)."""
-        if unit == "adamw":
-            return 0, self.a_begin, self.a_per, 0, self.a_padded
-        g = self._gmap[unit]
-        own = len(g["names"][self.rank]) * g["elems"]
-        return 1, g["base"] + self.rank * g["per"], own, g["base"], self.world * g["per"]
+    def _make_units(self, max_elems):
+        """AdamW first, then shape groups by descending size (the last unit's exchange or
+        copy-out is the one nothing overlaps, so the smallest goes last).  ``max_elems`` cuts
+        units into sub-ranges of at most that many elements (host pipelining)."""
+        units = []
+        R = self.rank
+        if max_elems is None:
+            units.append(("adamw", self.adamw, self.a_begin, self.a_end))
+        else:
+            step = max(64, max_elems // 64 * 64)
+            for lo in range(self.a_begin, self.a_end, step):
+                hi = min(lo + step, self.a_end)
+                pl = ResidentAdamW(self._adamw_tensors, grad_dtype=self.grad_dtype, rounding=self.rounding,
+                                   seed=self.seed, ctx=self.ctx)
+                pl.set_range(lo, hi)
+                self._sub_plans.append(pl)
+                units.append(("adamw", pl, lo, hi))
+        for g in sorted(self.groups, key=lambda g: -g["total"]):
+            mine = len(g["names"][R])
+            if not mine:
+                continue
+            gi, cap = self._pgroup[g["key"]]
+            per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
+            for first in range(0, mine, per):
+                units.append(("muon", gi, first, min(per, mine - first), g["key"]))
+        return units
+
+    def unit_span(self, unit):
+        """(arena index, element offset, element count) of the unit's span in the bf16
+        parameter / gradient arenas (arena 0 = AdamW, 1 = Muon)."""
+        if unit[0] == "adamw":
+            return 0, unit[2], unit[3] - unit[2]
+        g = self._gmap[unit[4]]
+        return 1, g["base"] + self.rank * g["per"] + unit[2] * g["elems"], unit[3] * g["elems"]
 
     # ---------------------------------------------------------------- the step
     def _compute_unit(self, unit, si):
         a, m = self.adamw_kw, self.muon_kw
-        if unit == "adamw":
+        if unit[0] == "adamw":
             tr = getattr(self, "trace_adamw", None)
             if tr is not None:                 # benchmark hook: CUDA events around the launch
                 e0, e1 = Event(), Event()
                 e0.record(si)
-            self.adamw.step(si, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=self.t)
+            unit[1].step(si, a["lr"], a["betas"][0], a["betas"][1], a["eps"], t=self.t)
             if tr is not None:
                 e1.record(si)
                 tr.append((e0, e1))
         else:
-            for ci in self._chunks[unit]:
-                self.muon.step_chunk(ci, si, m["lr"], m["momentum"], m["nesterov"], m["ns_steps"],
-                                     _schedule(self._sched))
+            self.muon.step_range(unit[1], unit[2], unit[3], si, m["lr"], m["momentum"], m["nesterov"],
+                                 m["ns_steps"], _schedule(self._sched))
 
     def _events(self, n):
         if not hasattr(self, "_evpool"):
@@ -231,7 +260,7 @@ class ResidentHybrid:
             for u, ev in zip(self.units, evs):
                 self._compute_unit(u, si)
                 ev.record(si)
-                arena, off, n, _, _ = self.unit_ranges(u)
+                arena, off, n = self.unit_span(u)
                 self.p2p.push(arena, off * 2, n * 2, ev)
             self.p2p.finish(si)
             return
@@ -274,7 +303,7 @@ class ResidentHybrid:
 
     def _h2d_unit(self, unit, stream):
         pa, pm, _ = self._pin_g
-        arena, off, n, _, _ = self.unit_ranges(unit)
+        arena, off, n = self.unit_span(unit)
         it = self._gdt.itemsize
         dev, host = (self.a_g, pa) if arena == 0 else (self.m_g, pm)
         if n:
@@ -284,7 +313,7 @@ class ResidentHybrid:
 
     def _d2h_unit(self, unit, stream):
         wa, wm = self._pin_w
-        arena, off, n, _, _ = self.unit_ranges(unit)
+        arena, off, n = self.unit_span(unit)
         dev, host = (self.a_p16, wa) if arena == 0 else (self.m_p16, wm)
         if n:
             L.check(L.lib().anc_d2h(self.ctx.handle, host.ptr + off * 2, dev.ptr + off * 2, n * 2,
@@ -307,6 +336,8 @@ class ResidentHybrid:
                 ss.append(s.value)
             self._streams = ss
         self.pinned_grads()
+        if self._host_units is None:
+            self._host_units = self._make_units(self.host_chunk_elems)
 
     def _weight_views(self):
         wa, wm = self._pin_w
@@ -328,7 +359,8 @@ class ResidentHybrid:
         self._stage_grads(grads)
         s_in, s_out = self._streams
         self.t += 1
-        nu = len(self.units)
+        units = self._host_units
+        nu = len(units)
         evs = self._events(3 * nu + 1)
         ev_in, ev_c, ev_out = evs[:nu], evs[nu:2 * nu], evs[2 * nu:3 * nu]
         start = evs[3 * nu]
@@ -338,14 +370,14 @@ class ResidentHybrid:
         L.check(lib.anc_stream_wait_event(s_out, start.handle))
         h2d = d2h = 0
         multi = self.world > 1
-        for k, u in enumerate(self.units):
+        for k, u in enumerate(units):
             h2d += self._h2d_unit(u, s_in)
             ev_in[k].record(s_in)
             L.check(lib.anc_stream_wait_event(si, ev_in[k].handle))
             self._compute_unit(u, si)
             ev_c[k].record(si)
             if multi and self.p2p is not None:
-                arena, off, n, _, _ = self.unit_ranges(u)
+                arena, off, n = self.unit_span(u)
                 self.p2p.push(arena, off * 2, n * 2, ev_c[k])
             L.check(lib.anc_stream_wait_event(s_out, ev_c[k].handle))
             d2h += self._d2h_unit(u, s_out)
@@ -404,6 +436,9 @@ class ResidentHybrid:
             self.p2p.destroy()
             self.p2p = None
         self.adamw.free()
+        for pl in self._sub_plans:
+            pl.free()
+        self._sub_plans = []
         if self.muon is not None:
             self.muon.free()
             self.muon = None

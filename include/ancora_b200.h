@@ -170,17 +170,18 @@ ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, i
  * rounding (muon.py:176,200). */
 ANC_API int anc_muon_step(anc_muon_plan *plan, double lr, float momentum, int nesterov, int ns_steps,
                           const float *coeffs, float eps, void *stream);
-/* The step is a sequence of chunks (one shape group, at most max_batch matrices) that run
- * one after another through the shared scratch.  These calls expose the chunks so a caller
- * can overlap each chunk's input copy / output copy / exchange with the next chunk's
- * compute using its own streams and events.  info = {index of the chunk's first weight among
- * the weights this plan steps (registration order), matrix count, M, N}.  Chunks must be
- * issued on ONE stream in any order that covers each exactly once per step. */
-ANC_API int anc_muon_plan_num_chunks(anc_muon_plan *plan, int *n);
-ANC_API int anc_muon_plan_chunk_info(anc_muon_plan *plan, int chunk, int32_t info[4]);
-ANC_API int anc_muon_step_chunk(anc_muon_plan *plan, int chunk, double lr, float momentum,
-                                int nesterov, int ns_steps, const float *coeffs, float eps,
-                                void *stream);
+/* The weights of a plan form shape groups (same Newton-Schulz shape), in order of first
+ * registration; inside a group the weights keep their registration order.  A caller can step
+ * any contiguous range of a group on its own -- to overlap that range's input copy, output
+ * copy or exchange with the next range's compute using its own streams and events.
+ * group_info = {weights in the group, largest range the scratch holds, M, N}.  Ranges share
+ * the scratch, so they must be issued on ONE stream; every weight once per step.  Results do
+ * not depend on how a group is cut into ranges. */
+ANC_API int anc_muon_plan_num_groups(anc_muon_plan *plan, int *n);
+ANC_API int anc_muon_plan_group_info(anc_muon_plan *plan, int group, int32_t info[4]);
+ANC_API int anc_muon_step_range(anc_muon_plan *plan, int group, int first, int count, double lr,
+                                float momentum, int nesterov, int ns_steps, const float *coeffs,
+                                float eps, void *stream);
 /* Per-phase device time accumulated over every anc_muon_step since the previous call
  * (timing enabled with anc_muon_plan_set_timing(plan, 1); CUDA events on the step's
  * stream, no synchronisation inside the step): ms spent in momentum, normalise,

@@ -101,3 +101,34 @@ def test_zero1_shards_bitwise_equal_single(ctx, world):
             assert np.array_equal(flat, full_master[n][2][s:e]), (r, n)
     for n, s in shp.items():
         assert covered[n] == int(np.prod(s)), n               # every element owned exactly once
+
+
+def test_step_host_pipeline_equals_plain_step(ctx):
+    """The pipelined host round trip (sub-chunked units on three streams) gives the same bits
+    as upload + step + download, and its returned views are the updated parameters."""
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=5)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    g1, g2 = S.synthetic_grads_bf16(shp, seed=6), S.synthetic_grads_bf16(shp, seed=7)
+    outs = []
+    for mode in ("plain", "host", "host_tiny_chunks"):
+        eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=9,
+                                 schedule=anc.PE_SCHEDULE, ctx=ctx)
+        if mode == "host_tiny_chunks":
+            eng.host_chunk_elems = 128 * 128 * 2          # two small matrices per unit
+        for g in (g1, g2):
+            if mode == "plain":
+                eng.upload_grads(g, ctx.stream)
+                eng.step(ctx.stream)
+                bits, _ = eng.download_weights_bits()
+            else:
+                bits, h2d, d2h = eng.step_host(g, ctx.stream)
+                assert h2d == d2h and h2d > 0
+        assert ctx.status() == 0
+        outs.append(({n: b.copy() for n, b in bits.items()}, eng.master()))
+        eng.free()
+    for other in outs[1:]:
+        for n in shp:
+            assert np.array_equal(outs[0][0][n], other[0][n]), n
+            assert np.array_equal(outs[0][1][n][2], other[1][n][2]), n
