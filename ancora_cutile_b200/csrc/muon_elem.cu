@@ -190,6 +190,8 @@ momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int ti
   // partial[slot * tiles_per_w + tile] = sum of squares of that 64x64 tile of bf16 u
   __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
   __shared__ float wsum[kThreads / 32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the packed operand may still be read by the previous launch
   const int total = n_w * tiles_per_w;
   for (int b = blockIdx.x; b < total; b += gridDim.x) {
     const int wi = b / tiles_per_w;
@@ -207,6 +209,8 @@ __global__ void __launch_bounds__(kThreads)
 fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip, int per_matrix,
                     float eps) {
   __shared__ float wsum[kThreads / 32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const float *pp = partial + (size_t)blockIdx.x * per_matrix;
   float acc = 0.f;
   for (int k = threadIdx.x; k < per_matrix; k += kThreads) acc = __fadd_rn(acc, pp[k]);
@@ -227,6 +231,8 @@ __global__ void __launch_bounds__(kThreads)
 update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, int tiles_per_w,
               float lr_scale_wide, float lr_scale_tall) {
   __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int total = n_w * tiles_per_w;
   for (int b = blockIdx.x; b < total; b += gridDim.x) {
     const int wi = b / tiles_per_w;
@@ -404,12 +410,27 @@ int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int
 static_assert(sizeof(anc_mom_entry) == sizeof(MomW), "table layout");
 static_assert(sizeof(anc_upd_entry) == sizeof(UpdW), "table layout");
 
+// Launch with programmatic stream serialization (the kernels above wait with griddepcontrol).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
                             float eps, cudaStream_t st) {
   (void)ctx;
   if (E <= 0) return ANC_OK;
-  fro_finalize_kernel<<<E, kThreads, 0, st>>>(partial, recip, per_matrix, eps);
-  ANC_CUDA(cudaGetLastError());
+  ANC_CUDA(launch_pdl(fro_finalize_kernel, E, st, partial, recip, per_matrix, eps));
   return ANC_OK;
 }
 
@@ -432,10 +453,11 @@ int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase
   int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
   if (grid == 0) return ANC_OK;
   if (grad_dtype == ANC_GRAD_F32)
-    momentum_kernel<true><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov, partial);
+    ANC_CUDA(launch_pdl(momentum_kernel<true>, grid, st, (const MomW *)d_table, xbase, n_w, tpw, momentum,
+                        nesterov, partial));
   else
-    momentum_kernel<false><<<grid, kThreads, 0, st>>>((const MomW *)d_table, xbase, n_w, tpw, momentum, nesterov, partial);
-  ANC_CUDA(cudaGetLastError());
+    ANC_CUDA(launch_pdl(momentum_kernel<false>, grid, st, (const MomW *)d_table, xbase, n_w, tpw, momentum,
+                        nesterov, partial));
   return ANC_OK;
 }
 
@@ -446,9 +468,8 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *o
   const long long total = (long long)n_w * tpw;
   int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
   if (grid == 0) return ANC_OK;
-  update_kernel<<<grid, kThreads, 0, st>>>((const UpdW *)d_table, obase, n_w, tpw, lr_scale_wide,
-                                            lr_scale_tall);
-  ANC_CUDA(cudaGetLastError());
+  ANC_CUDA(launch_pdl(update_kernel, grid, st, (const UpdW *)d_table, obase, n_w, tpw, lr_scale_wide,
+                      lr_scale_tall));
   return ANC_OK;
 }
 

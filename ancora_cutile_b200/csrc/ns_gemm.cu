@@ -128,6 +128,14 @@ __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch: the next kernel on the stream may be scheduled while this one
+// still runs; it blocks in pdl_wait() until every earlier grid has completed and its writes
+// are visible.  Hides the launch latency between the chained phases.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte
 // offsets (all >> 4), version 1, 128-byte swizzle.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -188,6 +196,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();                       // operands were written by the previous launch
 
   const bool nmajor_b = (p.mode == 2);
 
@@ -493,6 +503,8 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cluster_sync_all();                // both CTAs' barriers exist before any remote signal
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();                        // operands were written by the previous launch
   const bool nmajor_b = (p.mode == 2);
 
   if (warp == 0) {
@@ -855,13 +867,15 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes2;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     CUtensorMap tmC, tmD;
     rc = make_map(&tmC, C, (uint64_t)E * M, (uint64_t)p.ldc, 128);
     if (rc) return rc;
@@ -871,8 +885,17 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
     return ANC_OK;
   }
   int grid = p.total_tiles < ctx->sm_count ? p.total_tiles : ctx->sm_count;
-  ns_gemm_kernel<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, p);
-  ANC_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ANC_CUDA(cudaLaunchKernelEx(&cfg, ns_gemm_kernel, tmA, tmB, p));
   return ANC_OK;
 }
 
