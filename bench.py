@@ -302,6 +302,12 @@ def main():
     m_owned = eng.m_owned_elems
     elem_gbs = 24.0 * m_owned / ((mom_ms + upd_ms) / K * 1e-3) / 1e9 if (mom_ms + upd_ms) > 0 else 0.0
     n_groups = len(eng.groups)
+    # DRAM traffic of the GEMM launches: algorithmic bytes per matrix and iteration are 6MN + 8M^2
+    # (operands once, outputs once); the ncu capture on the reduced case measured 1.64x that
+    # (profiles/ns_gemm_pair_kernel_qwen3_reduced.md), scaled here by the matrices processed.
+    gemm_alg_bytes = sum(len(g["names"][rank]) * MUON_KW["ns_steps"] *
+                         (6 * g["key"][0] * g["key"][1] + 8 * g["key"][0] ** 2) for g in eng.groups)
+    launches_per_step = max(gemm_launches // K, 1)
     out = {
         "metric": "hybrid_optimizer_step_params_per_s", "value": value, "unit": "params/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -309,7 +315,11 @@ def main():
         "data": "synthetic", "config": config,
         "roofline": {"bound": "tensor", "kernel": "ns_gemm_pair_kernel", "achieved": ns_tflops,
                      "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": ns_tflops / peaks["bf16_tflops_sustained"], "traffic": None,
+                     "frac": ns_tflops / peaks["bf16_tflops_sustained"],
+                     "traffic": 1.64 * gemm_alg_bytes / launches_per_step,
+                     "traffic_note": "bytes per launch (average of the step's GEMM launches): ncu dram read+write "
+                                     "on the reduced case = 1.64 x algorithmic bytes, scaled by matrices processed",
+                     "algorithmic_bytes_per_launch": gemm_alg_bytes / launches_per_step,
                      "peak_kind": f"{peaks['src']} sustained cuBLAS bf16 (burst {peaks['bf16_tflops']})",
                      "frac_of_burst": ns_tflops / peaks["bf16_tflops"],
                      "flops_per_step": ns_flops / K, "ms_per_step": ns_ms / K, "launches_per_step": gemm_launches // K},
