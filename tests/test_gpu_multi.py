@@ -1,0 +1,106 @@
+"""GPU (needs >= 2 GPUs, skipped otherwise): the ZeRO-1 step on two real ranks, one process per
+GPU, with both exchange paths.  After the step every rank must hold, for every parameter, exactly
+the bf16 bits the single-GPU engine produces (BASELINE config 4: "bitwise identical to the 1-GPU
+result").  Ranks are plain child processes; the NCCL id and the IPC handles travel through gloo."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+AKW = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, wd=0.1)
+
+
+def _ngpu():
+    from ancora_cutile_b200 import _lib
+    n = C.c_int()
+    _lib.lib().anc_device_count(C.byref(n))
+    return n.value
+
+
+def _small():
+    from ancora_cutile_b200 import shapes as S
+    return S.qwen3_0_6b_shapes(n_layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=4096)
+
+
+def _run_engine(rank, world, mode, ctx, comm=None, all_gather=None):
+    import ancora_cutile_b200 as anc
+    from ancora_cutile_b200 import shapes as S
+    shp = _small()
+    params = S.synthetic_params(shp, seed=11)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=3,
+                             rank=rank, world=world, comm=comm, p2p=(mode == "p2p"),
+                             schedule=anc.PE_SCHEDULE, ctx=ctx)
+    if mode == "p2p":
+        eng.connect_p2p(all_gather(eng.p2p_handles()))
+    for k in range(3):
+        eng.upload_grads(S.synthetic_grads_bf16(shp, seed=20 + k), ctx.stream)
+        eng.step(ctx.stream)
+    ctx.sync()
+    status = ctx.status()
+    bits, _ = eng.download_weights_bits()
+    bits = {n: b.copy() for n, b in bits.items()}
+    return eng, bits, status
+
+
+def _worker(rank, world, port, mode, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    import ancora_cutile_b200 as anc
+    from ancora_cutile_b200.zero1 import Comm, nccl_unique_id
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    anc.set_device(rank)
+    ctx = anc.get_context()
+    comm = None
+    if mode == "nccl":
+        box = [nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = Comm(ctx, box[0], rank, world)
+
+    def all_gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    eng, bits, status = _run_engine(rank, world, mode, ctx, comm, all_gather)
+    dist.barrier()                      # nobody unmaps or frees while a peer may still push
+    q.put((rank, status, {n: b.tobytes() for n, b in bits.items()}))
+    dist.barrier()
+    eng.free()
+    if comm is not None:
+        comm.destroy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["p2p", "nccl"])
+def test_two_ranks_hold_the_single_gpu_bits(mode):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    import ancora_cutile_b200 as anc
+    ctx0 = anc.get_context()
+    eng, want, status = _run_engine(0, 1, "single", ctx0)
+    eng.free()
+    assert status == 0
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = 29600 + (os.getpid() % 1000) + (7 if mode == "nccl" else 0)
+    procs = [mpc.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    for rank, status, bits in got:
+        assert status == 0, (rank, status)
+        for n, w in want.items():
+            assert bits[n] == w.tobytes(), (mode, rank, n)
