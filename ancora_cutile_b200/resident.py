@@ -158,6 +158,7 @@ class ResidentHybrid:
         if p2p and W > 1:
             from .zero1 import P2PExchange
             self.p2p = P2PExchange(c, R, W, [self.a_p16.ptr, self.m_p16.ptr])
+            self.units = self._make_units(None, halve_from=8)
 
     # ---------------------------------------------------------------- exchange set-up
     def p2p_handles(self):
@@ -190,10 +191,12 @@ class ResidentHybrid:
             return (lo - o, hi - o) if lo < hi else (0, 0)
         return (0, n) if self.m_owner[name] == self.rank else (0, 0)
 
-    def _make_units(self, max_elems):
+    def _make_units(self, max_elems, halve_from=None):
         """AdamW first, then shape groups by descending size (the last unit's exchange or
         copy-out is the one nothing overlaps, so the smallest goes last).  ``max_elems`` cuts
-        units into sub-ranges of at most that many elements (host pipelining)."""
+        units into sub-ranges of at most that many elements (host pipelining); ``halve_from``
+        cuts a group with at least that many matrices of this rank in two, so that the first
+        half's exchange starts while the second half computes."""
         units = []
         R = self.rank
         if max_elems is None:
@@ -213,6 +216,8 @@ class ResidentHybrid:
                 continue
             gi, cap = self._pgroup[g["key"]]
             per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
+            if halve_from is not None and mine >= halve_from:
+                per = min(per, -(-mine // 2))
             for first in range(0, mine, per):
                 units.append(("muon", gi, first, min(per, mine - first), g["key"]))
         return units

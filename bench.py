@@ -280,9 +280,11 @@ def main():
     eng.trace_adamw = []                # CUDA events around each AdamW launch (no synchronisation)
     barrier()
     e0.record(ctx.stream)
+    t_issue = time.perf_counter()
     for k in range(args.steps):
         eng.step(ctx.stream)            # with N > 1 this includes the exchange of the bf16 parameters
     e1.record(ctx.stream)
+    host_issue_ms = (time.perf_counter() - t_issue) * 1e3 / args.steps   # time to ENQUEUE one step
     barrier()
     adamw_ms = sum(a0.elapsed_ms(a1) for a0, a1 in eng.trace_adamw)
     eng.trace_adamw = None
@@ -330,6 +332,7 @@ def main():
                              "frac": elem_gbs / peaks["hbm_gbs"], "bytes_per_param": 24,
                              "momentum_ms": mom_ms / K, "update_ms": upd_ms / K, "normalize_ms": nrm_ms / K},
         "clocks": clocks,
+        "host_issue_ms_per_step": host_issue_ms,
         # per step: 3 GEMM launches per iteration and group, momentum + finalize + update per group, AdamW
         "gpu_launches": (gemm_launches // K) + 3 * n_groups + 1,
         "state_bytes_per_gpu": eng.state_bytes() + (eng.muon.scratch_bytes() if eng.muon else 0),
