@@ -73,3 +73,22 @@ def test_two_ranks_agree_and_cover_everything():
     _, mu, _ = _muon_costs()
     assert sorted(box[0]["my_matrices"] + box[1]["my_matrices"]) == sorted(mu)
     assert not set(box[0]["my_matrices"]) & set(box[1]["my_matrices"])
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_partition_by_group_counts_and_balance(world):
+    from ancora_cutile_b200.zero1 import partition_by_group
+    for shp in (S.qwen3_0_6b_shapes(), S.moe_family_shapes()):
+        mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+        shapes = [shp[n] for n in mu]
+        owner, load = partition_by_group(shapes, world)
+        assert owner == partition_by_group(shapes, world)[0]
+        assert sum(load) == sum(ns_cost(*s) for s in shapes)
+        assert max(load) <= 1.03 * sum(load) / world
+        groups = {}
+        for s, o in zip(shapes, owner):
+            groups.setdefault((min(s), max(s)), []).append(o)
+        for key, owners in groups.items():
+            counts = [owners.count(r) for r in range(world)]
+            assert max(counts) - min(counts) <= 1, (key, counts)        # floor or ceil per rank
+            assert owners == sorted(owners)                              # contiguous runs in registration order
