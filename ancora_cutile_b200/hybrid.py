@@ -108,6 +108,13 @@ class HybridOptimizer:
             out[n] = flat.reshape(self.engine.shapes[n]) if (s, e) == (0, full) else flat
         return out
 
+    def state_dict(self):
+        """Resumable optimizer state of this rank (see ResidentHybrid.state_dict)."""
+        return self.engine.state_dict()
+
+    def load_state_dict(self, sd):
+        self.engine.load_state_dict(sd)
+
     def routing(self):
         return {"muon": list(self.muon_names), "adamw": list(self.adamw_names)}
 

@@ -431,6 +431,43 @@ class ResidentHybrid:
                     out[n] = (0, k, m32[self.m_own_off[n]:self.m_own_off[n] + k].copy())
         return out
 
+    # ---------------------------------------------------------------- save / resume
+    def state_dict(self):
+        """Everything needed to resume this rank bit-exactly: the fp32 arenas it owns, both
+        bf16 parameter arenas, the step counter and the SR seed, plus the layout facts a loader
+        checks.  (The reference has no optimizer-state save/load; its state is only readable
+        through master()/weights(), adamw.py:100-105.)"""
+        self.ctx.sync()
+        return {
+            "format": 1, "rank": self.rank, "world": self.world, "t": self.t, "seed": self.seed,
+            "grad_dtype": self.grad_dtype, "rounding": self.rounding,
+            "a_total": self.a_total, "a_begin": self.a_begin, "a_end": self.a_end, "m_total": self.m_total,
+            "names": list(self.adamw_names) + list(self.muon_names),
+            "a_p32": self.a_p32.to_numpy(), "a_m": self.a_m.to_numpy(), "a_v": self.a_v.to_numpy(),
+            "m_p32": self.m_p32.to_numpy(), "m_buf": self.m_buf.to_numpy(),
+            "a_p16": self.a_p16.to_numpy(), "m_p16": self.m_p16.to_numpy(),
+        }
+
+    def load_state_dict(self, sd):
+        """Restores a ``state_dict`` made by an engine built from the same parameter names and
+        shapes with the same world size and rank."""
+        want = dict(format=1, rank=self.rank, world=self.world, a_total=self.a_total, a_begin=self.a_begin,
+                    a_end=self.a_end, m_total=self.m_total, grad_dtype=self.grad_dtype, rounding=self.rounding,
+                    names=list(self.adamw_names) + list(self.muon_names))
+        for k, v in want.items():
+            if sd.get(k) != v:
+                raise ValueError(f"state_dict does not fit this engine: {k} is {sd.get(k)!r}, expected {v!r}")
+        for name in ("a_p32", "a_m", "a_v", "m_p32", "m_buf", "a_p16", "m_p16"):
+            buf, arr = getattr(self, name), np.ascontiguousarray(sd[name])
+            if arr.shape != tuple(buf.shape) or arr.dtype != buf.dtype:
+                raise ValueError(f"state_dict[{name}] has shape {arr.shape} {arr.dtype}")
+            buf.upload(arr)
+        self.t = int(sd["t"])
+        self.seed = int(sd["seed"])
+        self.adamw.seed = self.seed
+        for pl in self._sub_plans:
+            pl.seed = self.seed
+
     def state_bytes(self):
         return sum(b.nbytes for b in (self.a_p16, self.a_g, self.a_p32, self.a_m, self.a_v,
                                       self.m_p16, self.m_g, self.m_p32, self.m_buf))

@@ -132,3 +132,37 @@ def test_step_host_pipeline_equals_plain_step(ctx):
         for n in shp:
             assert np.array_equal(outs[0][0][n], other[0][n]), n
             assert np.array_equal(outs[0][1][n][2], other[1][n][2]), n
+
+
+def test_state_dict_resume_is_bit_exact(ctx):
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=8)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    gs = [S.synthetic_grads_bf16(shp, seed=30 + k) for k in range(4)]
+    mk = lambda p: anc.ResidentHybrid(p, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=21,
+                                      schedule=anc.PE_SCHEDULE, ctx=ctx)
+    a = mk(params)
+    for g in gs[:2]:
+        a.upload_grads(g, ctx.stream); a.step(ctx.stream)
+    sd = a.state_dict()
+    for g in gs[2:]:
+        a.upload_grads(g, ctx.stream); a.step(ctx.stream)
+    want_bits, _ = a.download_weights_bits()
+    want_bits = {n: b.copy() for n, b in want_bits.items()}
+    want_master = a.master()
+    a.free()
+    # a fresh engine built from unrelated initial values, then restored
+    b = mk({n: np.zeros_like(p) for n, p in params.items()})
+    b.load_state_dict(sd)
+    assert b.t == 2
+    for g in gs[2:]:
+        b.upload_grads(g, ctx.stream); b.step(ctx.stream)
+    got_bits, _ = b.download_weights_bits()
+    for n in shp:
+        assert np.array_equal(got_bits[n], want_bits[n]), n
+        assert np.array_equal(b.master()[n][2], want_master[n][2]), n
+    with pytest.raises(ValueError):
+        sd2 = dict(sd); sd2["world"] = 2
+        b.load_state_dict(sd2)
+    b.free()
