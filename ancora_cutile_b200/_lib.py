@@ -32,6 +32,10 @@ class AdamWScalars(C.Structure):
                 ("beta1", "one_minus_beta1", "beta2", "one_minus_beta2", "eps", "lr", "ibc1", "ibc2")]
 
 
+class MuonOutputs(C.Structure):
+    _fields_ = [("fp8", C.c_void_p), ("fp8_scale", C.c_void_p), ("p16_t", C.c_void_p)]
+
+
 class MuonWeight(C.Structure):
     _fields_ = [("buf", C.c_void_p), ("g", C.c_void_p), ("p32", C.c_void_p), ("p16", C.c_void_p),
                 ("K", C.c_int32), ("N", C.c_int32), ("owner", C.c_int32), ("_pad", C.c_int32)]
@@ -73,6 +77,7 @@ SIGNATURES = {
     "anc_adamw_step": (_i, [_vp, C.POINTER(AdamWScalars), _i, _u64, _u64, _vp]),
     "anc_adamw_plan_destroy": (_i, [_vp]),
     "anc_muon_plan_create": (_i, [_vp, C.POINTER(MuonWeight), _i, _i, _i, _i, _pp]),
+    "anc_muon_plan_create_ex": (_i, [_vp, C.POINTER(MuonWeight), C.POINTER(MuonOutputs), _i, _i, _i, _i, _pp]),
     "anc_muon_step": (_i, [_vp, _d, _f, _i, _i, C.POINTER(_f), _f, _vp]),
     "anc_muon_plan_num_groups": (_i, [_vp, C.POINTER(_i)]),
     "anc_muon_plan_group_info": (_i, [_vp, _i, C.POINTER(C.c_int32)]),

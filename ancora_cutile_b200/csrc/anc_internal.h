@@ -22,6 +22,7 @@ struct anc_ctx {
 // entries of the device tables the Muon plan builds for the group launches
 struct anc_mom_entry { float *buf; const void *g; int K, N, tr, _pad; };
 struct anc_upd_entry { float *p32; uint16_t *p16; int K, N, tr, _pad; };
+struct anc_upd_extra { uint8_t *fp8; uint8_t *scale; uint16_t *p16_t; int64_t _pad; };
 
 // device status bits
 #define ANC_DEV_TIMEOUT_TMA 0x1u     // producer/consumer mbarrier wait ran out
@@ -78,8 +79,8 @@ int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, in
                             float eps, cudaStream_t st);
 int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int E, int M, int N,
                            cudaStream_t st);
-int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *obase, int n_w,
-                            int elems_per_w, float lr_scale_wide, float lr_scale_tall,
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_extras, const uint16_t *obase,
+                            int n_w, int elems_per_w, float lr_scale_wide, float lr_scale_tall,
                             cudaStream_t st);
 // mscale (nullable): per-matrix factor r[e] folded into the epilogue -- mode 0 stores
 // RNE(r^2 * acc), mode 2 stores RNE((alpha*r)*Q + (beta*r)*acc); mode 1 ignores it.

@@ -243,6 +243,160 @@ update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, in
   }
 }
 
+// ---- update with post-step consumers fused in ---------------------------------------------
+// Optional extra outputs of the update, produced from the freshly rounded bf16 weight while it is
+// still on chip (the reference runs them as separate sweeps after every optimizer step):
+//   fp8 + scale : MXFP8 re-quantisation, blocks of 32 along K (rows), E8M0 scale byte =
+//                 max(exponent(amax) - 7, 0), value = RNE_e4m3(w / 2^(byte-127))
+//                 (ancora/kernels/quant.py:56-68 `_quant_mxfp8_w`; layout (K,N) u8 + (K/32,N) u8)
+//   p16_t       : the transposed bf16 copy (N,K) a backward pass reads
+//                 (ancora/kernels/moe.py:371-377 `_transpose_e`)
+struct UpdX {
+  uint8_t *fp8;
+  uint8_t *scale;
+  uint16_t *p16_t;
+  int64_t _pad;
+};
+
+__device__ __forceinline__ uint32_t e4m3_rn(float x) {
+  // cvt.rn.satfinite.e4m3x2.f32 packs two values; the high one is zero here
+  uint16_t r;
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %1, %2;\n\tmov.b16 %0, t;\n\t}" : "=h"(r) : "f"(0.f), "f"(x));
+  return (uint32_t)(r & 0xFF);
+}
+
+// 64x64 tile, same thread mapping as update_tile (8 columns x rows r0, r0+32): the two rows of a
+// thread fall into the tile's two 32-row quantisation blocks.
+__device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x, int slot,
+                                                   const uint16_t *obase, float lr_scale, int ti, int tj,
+                                                   uint16_t (*sm)[kTile + kPad], uint32_t (*wmax)[2][kTile],
+                                                   uint8_t (*sbyte)[kTile]) {
+  const uint16_t *wo = obase + (size_t)slot * w.K * w.N;
+  const int c8 = (threadIdx.x & 7) * 8;
+  const int r0 = threadIdx.x >> 3;
+  const int col = tj * kTile + c8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (w.tr) {
+    const int oc = threadIdx.x >> 2;
+    const int rr = (threadIdx.x & 3) * 16;
+    const uint16_t *src = wo + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+    reinterpret_cast<uint4 *>(&sm[oc][rr])[0] = reinterpret_cast<const uint4 *>(src)[0];
+    reinterpret_cast<uint4 *>(&sm[oc][rr])[1] = reinterpret_cast<const uint4 *>(src)[1];
+    __syncthreads();
+  }
+  uint32_t h[2][8];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int rl = r0 + 32 * k;
+    const size_t idx = (size_t)(ti * kTile + rl) * w.N + col;
+    const float4 p0 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
+    const float4 p1 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx) + 1);
+    float o[8];
+    if (!w.tr) {
+      const uint4 ov = *reinterpret_cast<const uint4 *>(wo + idx);
+      const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[2 * j] = __uint_as_float(ow[j] << 16);
+        o[2 * j + 1] = __uint_as_float(ow[j] & 0xFFFF0000u);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][rl]);
+    }
+    const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float pn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      pn[j] = __fsub_rn(pp[j], __fmul_rn(lr_scale, o[j]));
+      h[k][j] = rne16(pn[j]);
+    }
+    __stcs(reinterpret_cast<float4 *>(w.p32 + idx), make_float4(pn[0], pn[1], pn[2], pn[3]));
+    __stcs(reinterpret_cast<float4 *>(w.p32 + idx) + 1, make_float4(pn[4], pn[5], pn[6], pn[7]));
+    *reinterpret_cast<uint4 *>(w.p16 + idx) = make_uint4(h[k][0] | (h[k][1] << 16), h[k][2] | (h[k][3] << 16),
+                                                         h[k][4] | (h[k][5] << 16), h[k][6] | (h[k][7] << 16));
+  }
+  __syncthreads();                       // every thread is done reading the staged O^T tile
+  if (x.p16_t) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      *reinterpret_cast<uint4 *>(&sm[r0 + 32 * k][c8]) =
+          make_uint4(h[k][0] | (h[k][1] << 16), h[k][2] | (h[k][3] << 16), h[k][4] | (h[k][5] << 16),
+                     h[k][6] | (h[k][7] << 16));
+  }
+  if (x.fp8) {
+    // column maxima of |w| per 32-row block: 4 rows per warp by shuffles, 8 warps through smem
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t a = h[k][j] & 0x7FFFu;                 // |bf16| bits order like the magnitudes
+        a = max(a, __shfl_xor_sync(0xFFFFFFFFu, a, 8));
+        a = max(a, __shfl_xor_sync(0xFFFFFFFFu, a, 16));
+        if (lane < 8) wmax[warp][k][c8 + j] = a;
+      }
+  }
+  __syncthreads();
+  if (x.fp8 && threadIdx.x < 2 * kTile) {
+    const int k = threadIdx.x >> 6, c = threadIdx.x & 63;
+    uint32_t a = wmax[0][k][c];
+#pragma unroll
+    for (int q = 1; q < kThreads / 32; ++q) a = max(a, wmax[q][k][c]);
+    const uint32_t ea = (a >> 7) & 0xFF;                // exponent field of the bf16 = of the float
+    const uint32_t byte = ea >= 7 ? ea - 7 : 0;
+    sbyte[k][c] = (uint8_t)byte;
+    x.scale[((size_t)(ti * 2 + k)) * w.N + (size_t)tj * kTile + c] = (uint8_t)byte;
+  }
+  if (x.p16_t) {
+    // transposed store of the bf16 tile: thread handles output row t/4, 16 elements
+    const int oc = threadIdx.x >> 2;
+    const int rr = (threadIdx.x & 3) * 16;
+    uint32_t pk[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      pk[j] = (uint32_t)sm[rr + 2 * j][oc] | ((uint32_t)sm[rr + 2 * j + 1][oc] << 16);
+    uint16_t *dst = x.p16_t + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+    reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+  }
+  __syncthreads();
+  if (x.fp8) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      uint32_t q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t byte = sbyte[k][c8 + j];
+        const float inv = __uint_as_float((254u - byte) << 23);      // 2^(127 - byte), exact
+        q[j] = e4m3_rn(__fmul_rn(bf16_f32(h[k][j]), inv));
+      }
+      const size_t idx = (size_t)(ti * kTile + r0 + 32 * k) * w.N + col;
+      *reinterpret_cast<uint2 *>(x.fp8 + idx) =
+          make_uint2(q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24), q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24));
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads)
+update_extras_kernel(const UpdW *__restrict__ table, const UpdX *__restrict__ extras, const uint16_t *obase,
+                     int n_w, int tiles_per_w, float lr_scale_wide, float lr_scale_tall) {
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ uint32_t wmax[kThreads / 32][2][kTile];
+  __shared__ uint8_t sbyte[2][kTile];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int total = n_w * tiles_per_w;
+  for (int b = blockIdx.x; b < total; b += gridDim.x) {
+    const int wi = b / tiles_per_w;
+    const int t = b - wi * tiles_per_w;
+    const UpdW w = table[wi];
+    const UpdX x = extras[wi];
+    const int tn = w.N / kTile;
+    update_tile_extras(w, x, wi, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm, wmax, sbyte);
+  }
+}
+
 // single-weight forms (table passed by value)
 template <bool kGradF32>
 __global__ void __launch_bounds__(kThreads)
@@ -461,9 +615,20 @@ int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase
   return ANC_OK;
 }
 
-int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const uint16_t *obase, int n_w,
-                            int elems_per_w, float lr_scale_wide, float lr_scale_tall,
+static_assert(sizeof(anc_upd_extra) == sizeof(UpdX), "table layout");
+
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_extras, const uint16_t *obase,
+                            int n_w, int elems_per_w, float lr_scale_wide, float lr_scale_tall,
                             cudaStream_t st) {
+  if (d_extras) {
+    const int tpw = elems_per_w / (kTile * kTile);
+    const long long total = (long long)n_w * tpw;
+    int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
+    if (grid == 0) return ANC_OK;
+    ANC_CUDA(launch_pdl(update_extras_kernel, grid, st, (const UpdW *)d_table, (const UpdX *)d_extras, obase,
+                        n_w, tpw, lr_scale_wide, lr_scale_tall));
+    return ANC_OK;
+  }
   const int tpw = elems_per_w / (kTile * kTile);
   const long long total = (long long)n_w * tpw;
   int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);

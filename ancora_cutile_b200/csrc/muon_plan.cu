@@ -19,6 +19,7 @@ struct Group {
   std::vector<int> widx;           // plan weight indices, in registration order
   anc_mom_entry *d_mom = nullptr;  // device tables, one entry per weight
   anc_upd_entry *d_upd = nullptr;
+  anc_upd_extra *d_ext = nullptr;  // optional extra outputs of the update (nullptr: none in this group)
   double scale_tall = 1.0;         // sqrt(max(1, K/N)) for the K > N members
 };
 
@@ -34,6 +35,7 @@ struct anc_muon_plan {
   int grad_dtype;
   int max_batch;
   std::vector<anc_muon_weight> weights;   // owned weights only
+  std::vector<anc_muon_outputs> outputs;  // parallel to weights (all-null entries when unused)
   std::vector<Group> groups;
   uint16_t *X = nullptr, *Y = nullptr, *A = nullptr, *B = nullptr;
   float *recip = nullptr;
@@ -68,6 +70,7 @@ static void plan_free(anc_muon_plan *pl) {
   for (auto &g : pl->groups) {
     if (g.d_mom) cudaFree(g.d_mom);
     if (g.d_upd) cudaFree(g.d_upd);
+    if (g.d_ext) cudaFree(g.d_ext);
   }
   for (void *p : {(void *)pl->X, (void *)pl->Y, (void *)pl->A, (void *)pl->B, (void *)pl->recip,
                   (void *)pl->partial})
@@ -83,6 +86,12 @@ extern "C" {
 
 int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_weights, int grad_dtype,
                          int my_rank, int max_batch, anc_muon_plan **out) {
+  return anc_muon_plan_create_ex(ctx, weights, nullptr, n_weights, grad_dtype, my_rank, max_batch, out);
+}
+
+int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const anc_muon_outputs *outputs,
+                            int n_weights, int grad_dtype, int my_rank, int max_batch,
+                            anc_muon_plan **out) {
   ANC_REQUIRE(ctx && out && (weights || n_weights == 0), "NULL argument");
   ANC_REQUIRE(grad_dtype == ANC_GRAD_BF16 || grad_dtype == ANC_GRAD_F32, "bad grad_dtype");
   *out = nullptr;
@@ -119,6 +128,14 @@ int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_wei
     }
     pl->groups[it->second].widx.push_back((int)pl->weights.size());
     pl->weights.push_back(w);
+    anc_muon_outputs o = {nullptr, nullptr, nullptr};
+    if (outputs) o = outputs[i];
+    if ((o.fp8 == nullptr) != (o.fp8_scale == nullptr)) {
+      anc_set_error("Muon weight %d: fp8 and fp8_scale must be given together", i);
+      plan_free(pl);
+      return ANC_E_INVALID;
+    }
+    pl->outputs.push_back(o);
   }
   // scratch: sized for the largest batch over all groups
   size_t xe = 0, ae = 0, emax = 0;
@@ -129,10 +146,24 @@ int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_wei
     emax = std::max(emax, E);
     std::vector<anc_mom_entry> mom;
     std::vector<anc_upd_entry> upd;
+    std::vector<anc_upd_extra> ext;
+    bool any_ext = false;
     for (size_t s = 0; s < g.widx.size(); ++s) {
       const anc_muon_weight &w = pl->weights[g.widx[s]];
       mom.push_back({w.buf, w.g, w.K, w.N, w.K > w.N ? 1 : 0, 0});
       upd.push_back({w.p32, w.p16, w.K, w.N, w.K > w.N ? 1 : 0, 0});
+      const anc_muon_outputs &o = pl->outputs[g.widx[s]];
+      ext.push_back({o.fp8, o.fp8_scale, o.p16_t, 0});
+      any_ext = any_ext || o.fp8 || o.p16_t;
+    }
+    if (any_ext) {
+      cudaError_t ee = cudaMalloc((void **)&g.d_ext, ext.size() * sizeof(anc_upd_extra));
+      if (ee == cudaSuccess)
+        ee = cudaMemcpy(g.d_ext, ext.data(), ext.size() * sizeof(anc_upd_extra), cudaMemcpyHostToDevice);
+      if (ee != cudaSuccess) {
+        plan_free(pl);
+        return anc_cuda_fail(ee, "muon output table");
+      }
     }
     cudaError_t e = cudaMalloc((void **)&g.d_mom, mom.size() * sizeof(anc_mom_entry));
     if (e == cudaSuccess) e = cudaMalloc((void **)&g.d_upd, upd.size() * sizeof(anc_upd_entry));
@@ -225,7 +256,8 @@ int step_chunk(anc_muon_plan *pl, const ChunkRef &c, double lr, float momentum, 
       (double)E * ns_steps * (4.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M);
   pl->last_launches += 3 * ns_steps;
   begin_span(3);
-  rc = anc_launch_update_group(ctx, g.d_upd + c.w0, X, E, epw, scale_wide, scale_tall, st);
+  rc = anc_launch_update_group(ctx, g.d_upd + c.w0, g.d_ext ? (const void *)(g.d_ext + c.w0) : nullptr, X, E,
+                               epw, scale_wide, scale_tall, st);
   end_span();
   return rc;
 }

@@ -34,13 +34,16 @@ class MuonPlan:
     def __init__(self, weights, grad_dtype="f32", my_rank=0, max_batch=0, ctx=None):
         self.ctx = ctx or get_context()
         arr = (L.MuonWeight * max(len(weights), 1))()
+        outs = (L.MuonOutputs * max(len(weights), 1))()
         for i, w in enumerate(weights):
             _check_aligned(w["K"], w["N"])
             arr[i] = L.MuonWeight(dev_ptr(w["buf"]), dev_ptr(w["G"]), dev_ptr(w["p32"]), dev_ptr(w["p16"]),
                                   int(w["K"]), int(w["N"]), int(w.get("owner", -1)), 0)
+            # optional fused post-step outputs: MXFP8 re-quant (fp8 + fp8_scale), transposed bf16 copy
+            outs[i] = L.MuonOutputs(dev_ptr(w.get("fp8")), dev_ptr(w.get("fp8_scale")), dev_ptr(w.get("p16_t")))
         h = C.c_void_p()
-        L.check(L.lib().anc_muon_plan_create(self.ctx.handle, arr, len(weights), _GRAD[grad_dtype],
-                                             int(my_rank), int(max_batch or 0), C.byref(h)))
+        L.check(L.lib().anc_muon_plan_create_ex(self.ctx.handle, arr, outs, len(weights), _GRAD[grad_dtype],
+                                                int(my_rank), int(max_batch or 0), C.byref(h)))
         self.handle = h
 
     def step(self, si, lr, momentum, nesterov, ns_steps, schedule, eps=1e-7):

@@ -160,6 +160,22 @@ typedef struct anc_muon_weight {
  * max_batch <= 0 batches a whole shape group at once. */
 ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, int n_weights,
                                  int grad_dtype, int my_rank, int max_batch, anc_muon_plan **out);
+/* Optional extra outputs the update writes from the freshly rounded bf16 weight (all
+ * pointers may be NULL).  They replace sweeps the reference runs after every optimizer
+ * step: the MXFP8 re-quantisation of the projection weights (ancora/kernels/quant.py:56-68
+ * `_quant_mxfp8_w`, re-run because the step dirties them, model/resident_train.py:190-199,
+ * 354-357) and the transposed expert weights for the backward (kernels/moe.py:371-377,593-596).
+ *   fp8       (K,N) u8  E4M3 values, quantisation blocks of 32 along K
+ *   fp8_scale (K/32,N) u8  E8M0 bytes: max(exponent(max|w| of the block) - 7, 0)
+ *   p16_t     (N,K) bf16  transposed copy of p16 */
+typedef struct anc_muon_outputs {
+  uint8_t *fp8;
+  uint8_t *fp8_scale;
+  uint16_t *p16_t;
+} anc_muon_outputs;
+ANC_API int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights,
+                                    const anc_muon_outputs *outputs, int n_weights, int grad_dtype,
+                                    int my_rank, int max_batch, anc_muon_plan **out);
 /* One Muon step for every owned weight: momentum + Nesterov -> packed bf16 u
  * (transposed for tall weights) -> Frobenius normalisation -> ns_steps Newton-Schulz
  * iterations with coeffs[k] = (a,b,c) -> master update + bf16 refresh.  Replaces

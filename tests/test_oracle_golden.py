@@ -5,7 +5,7 @@ import os
 
 import numpy as np
 
-from oracle import adamw_ref, bf16, muon_ref, philox
+from oracle import adamw_ref, bf16, muon_ref, philox, quant_ref
 
 G = os.path.join(os.path.dirname(__file__), "golden")
 
@@ -133,3 +133,14 @@ def test_bf16_chain_model_within_tolerance():
         want = muon_ref.ns_fp32(bf16.bits_f32(g), 5, muon_ref.PE_SCHEDULE)
         got = bf16.bits_f32(muon_ref.ns_bf16_chain(g, 5, muon_ref.PE_SCHEDULE))
         assert _rel(got, want) < 2e-2
+
+
+def test_oracle_quant_decodes_within_e4m3_step():
+    rng = np.random.default_rng(0)
+    w = bf16.rne_bits((rng.standard_normal((128, 96)) * np.exp(rng.uniform(-8, 2, (1, 96)))).astype(np.float32))
+    q, byte = quant_ref.quant_mxfp8_w(w)
+    back = quant_ref.dequant_mxfp8_w(q, byte)
+    x = bf16.bits_f32(w).astype(np.float64)
+    blockmax = np.abs(x).reshape(4, 32, 96).max(axis=1).repeat(32, axis=0)
+    assert np.all(np.abs(back - x) <= blockmax * 2.0 ** -4 + 1e-30)       # 3 mantissa bits, block-relative
+    assert np.all(q[np.abs(x) == blockmax] != 0)
