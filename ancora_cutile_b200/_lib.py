@@ -67,6 +67,10 @@ SIGNATURES = {
     "anc_event_sync": (_i, [_vp]),
     "anc_event_elapsed_ms": (_i, [_vp, _vp, C.POINTER(_f)]),
     "anc_event_destroy": (_i, [_vp]),
+    "anc_graph_begin": (_i, [_vp, _vp]),
+    "anc_graph_end": (_i, [_vp, _vp, _pp]),
+    "anc_graph_launch": (_i, [_vp, _vp, _vp]),
+    "anc_graph_destroy": (_i, [_vp]),
     "anc_stream_create": (_i, [_vp, _pp]),
     "anc_stream_destroy": (_i, [_vp, _vp]),
     "anc_stream_wait_event": (_i, [_vp, _vp]),
@@ -75,6 +79,8 @@ SIGNATURES = {
     "anc_adamw_plan_set_range": (_i, [_vp, _u64, _u64]),
     "anc_adamw_plan_total": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "anc_adamw_step": (_i, [_vp, C.POINTER(AdamWScalars), _i, _u64, _u64, _vp]),
+    "anc_adamw_plan_set_schedule": (_i, [_vp, C.POINTER(AdamWScalars), _i, _u64]),
+    "anc_adamw_step_scheduled": (_i, [_vp, _i, _u64, _i, _vp]),
     "anc_adamw_plan_destroy": (_i, [_vp]),
     "anc_muon_plan_create": (_i, [_vp, C.POINTER(MuonWeight), _i, _i, _i, _i, _pp]),
     "anc_muon_plan_create_ex": (_i, [_vp, C.POINTER(MuonWeight), C.POINTER(MuonOutputs), _i, _i, _i, _i, _pp]),
@@ -97,6 +103,7 @@ SIGNATURES = {
     "anc_comm_create": (_i, [_vp, _vp, _i, _i, _pp]),
     "anc_comm_destroy": (_i, [_vp]),
     "anc_comm_allgather_bf16": (_i, [_vp, _vp, _u64, _vp]),
+    "anc_comm_reduce_scatter_grads": (_i, [_vp, _vp, _u64, _i, _vp]),
     "anc_comm_bcast_segments": (_i, [_vp, _pp, C.POINTER(_u64), C.POINTER(_i), _i, _vp]),
     "anc_comm_barrier": (_i, [_vp, _vp]),
     "anc_ipc_export_mem": (_i, [_vp, _vp, _vp]),

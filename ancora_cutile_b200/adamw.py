@@ -94,6 +94,17 @@ class ResidentAdamW:
         L.check(L.lib().anc_adamw_step(self.handle, C.byref(s), _ROUND[self.rounding], self.seed, int(t),
                                        C.c_void_p(si or None)))
 
+    def set_schedule(self, first_step, n, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8):
+        """Uploads the scalars of steps first_step .. first_step+n-1 and sets the device step
+        counter to first_step (for ``step_scheduled`` / graph replay)."""
+        tab = (L.AdamWScalars * n)(*[step_scalars(lr, b1, b2, eps, first_step + k) for k in range(n)])
+        L.check(L.lib().anc_adamw_plan_set_schedule(self.handle, tab, n, int(first_step)))
+
+    def step_scheduled(self, si=None, advance=True):
+        """The step whose number is in the device counter; capturable in a CUDA graph."""
+        L.check(L.lib().anc_adamw_step_scheduled(self.handle, _ROUND[self.rounding], self.seed,
+                                                 int(bool(advance)), C.c_void_p(si or None)))
+
     def free(self):
         if self.handle:
             L.lib().anc_adamw_plan_destroy(self.handle)

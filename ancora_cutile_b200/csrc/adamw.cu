@@ -101,7 +101,22 @@ template <bool kGradF32, bool kSR>
 __global__ void __launch_bounds__(kThreads)
 adamw_multi_kernel(const TensorEntry *__restrict__ tensors, const Chunk *__restrict__ chunks,
                    uint32_t n_chunks, uint32_t n_tensors, Scalars s, uint32_t seed_lo,
-                   uint32_t seed_hi, uint32_t step_lo, uint32_t step_hi, uint32_t *status) {
+                   uint32_t seed_hi, uint32_t step_lo, uint32_t step_hi, uint32_t *status,
+                   const Scalars *__restrict__ sched, const unsigned long long *__restrict__ counter,
+                   unsigned long long sched_first, uint32_t sched_len) {
+  if (sched) {
+    // device-resident schedule: the step number lives in device memory and selects this step's
+    // scalars from a table the host filled in advance, so the launch can be replayed from a graph
+    const unsigned long long t = *counter;
+    const unsigned long long k = t - sched_first;
+    if (k >= sched_len) {
+      if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, ANC_DEV_BAD_INDEX);
+      return;
+    }
+    s = sched[k];
+    step_lo = (uint32_t)t;
+    step_hi = (uint32_t)(t >> 32);
+  }
   for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
     const Chunk ch = chunks[c];
     if (ch.tensor >= n_tensors) {   // table corruption guard: record and skip
@@ -178,6 +193,8 @@ adamw_multi_kernel(const TensorEntry *__restrict__ tensors, const Chunk *__restr
   }
 }
 
+__global__ void adamw_advance_kernel(unsigned long long *counter) { *counter += 1ull; }
+
 }  // namespace
 
 struct anc_adamw_plan {
@@ -190,6 +207,10 @@ struct anc_adamw_plan {
   Chunk *d_chunks;
   uint32_t n_chunks;
   uint32_t chunk_capacity;
+  Scalars *d_sched = nullptr;              // optional device-resident schedule
+  unsigned long long *d_counter = nullptr;
+  unsigned long long sched_first = 0;
+  uint32_t sched_len = 0;
 };
 
 static int adamw_build_chunks(anc_adamw_plan *pl, uint64_t begin, uint64_t end) {
@@ -318,7 +339,7 @@ int anc_adamw_step(anc_adamw_plan *plan, const anc_adamw_scalars *sc, int roundi
 #define ANC_ADAMW_LAUNCH(F32, SR)                                                              \
   adamw_multi_kernel<F32, SR><<<grid, kThreads, 0, st>>>(plan->d_tensors, plan->d_chunks,      \
                                                          plan->n_chunks, nt, s, sl, sh, tl, th, \
-                                                         ctx->d_status)
+                                                         ctx->d_status, nullptr, nullptr, 0ull, 0u)
   const bool f32 = plan->grad_dtype == ANC_GRAD_F32;
   const bool sr = rounding == ANC_ROUND_SR;
   if (f32 && sr) ANC_ADAMW_LAUNCH(true, true);
@@ -330,10 +351,65 @@ int anc_adamw_step(anc_adamw_plan *plan, const anc_adamw_scalars *sc, int roundi
   return ANC_OK;
 }
 
+int anc_adamw_plan_set_schedule(anc_adamw_plan *plan, const anc_adamw_scalars *table, int n,
+                                uint64_t first_step) {
+  ANC_REQUIRE(plan && table && n > 0, "bad argument");
+  anc_device_guard guard(plan->ctx->device);
+  ANC_CUDA(cudaStreamSynchronize(plan->ctx->stream));
+  if (plan->d_sched) cudaFree(plan->d_sched);
+  plan->d_sched = nullptr;
+  static_assert(sizeof(Scalars) == sizeof(anc_adamw_scalars), "scalar layout");
+  ANC_CUDA(cudaMalloc((void **)&plan->d_sched, sizeof(Scalars) * (size_t)n));
+  ANC_CUDA(cudaMemcpy(plan->d_sched, table, sizeof(Scalars) * (size_t)n, cudaMemcpyHostToDevice));
+  if (!plan->d_counter) ANC_CUDA(cudaMalloc((void **)&plan->d_counter, sizeof(unsigned long long)));
+  unsigned long long t0 = first_step;
+  ANC_CUDA(cudaMemcpy(plan->d_counter, &t0, sizeof(t0), cudaMemcpyHostToDevice));
+  plan->sched_first = first_step;
+  plan->sched_len = (uint32_t)n;
+  return ANC_OK;
+}
+
+int anc_adamw_step_scheduled(anc_adamw_plan *plan, int rounding, uint64_t seed, int advance,
+                             void *stream) {
+  ANC_REQUIRE(plan, "plan is NULL");
+  ANC_REQUIRE(plan->d_sched && plan->d_counter, "no schedule: call anc_adamw_plan_set_schedule first");
+  ANC_REQUIRE(rounding == ANC_ROUND_RNE || rounding == ANC_ROUND_SR, "bad rounding %d", rounding);
+  anc_ctx *ctx = plan->ctx;
+  anc_device_guard guard(ctx->device);
+  cudaStream_t st = anc_pick_stream(ctx, stream);
+  if (plan->n_chunks) {
+    Scalars s = {};
+    uint32_t grid = plan->n_chunks;
+    const uint32_t cap = (uint32_t)ctx->sm_count * 16u;
+    if (grid > cap) grid = cap;
+    const uint32_t nt = (uint32_t)plan->tensors.size();
+    const uint32_t sl = (uint32_t)seed, sh = (uint32_t)(seed >> 32);
+#define ANC_ADAMW_LAUNCH_S(F32, SR)                                                                 \
+  adamw_multi_kernel<F32, SR><<<grid, kThreads, 0, st>>>(                                           \
+      plan->d_tensors, plan->d_chunks, plan->n_chunks, nt, s, sl, sh, 0u, 0u, ctx->d_status,        \
+      plan->d_sched, plan->d_counter, plan->sched_first, plan->sched_len)
+    const bool f32 = plan->grad_dtype == ANC_GRAD_F32;
+    const bool sr = rounding == ANC_ROUND_SR;
+    if (f32 && sr) ANC_ADAMW_LAUNCH_S(true, true);
+    else if (f32) ANC_ADAMW_LAUNCH_S(true, false);
+    else if (sr) ANC_ADAMW_LAUNCH_S(false, true);
+    else ANC_ADAMW_LAUNCH_S(false, false);
+#undef ANC_ADAMW_LAUNCH_S
+    ANC_CUDA(cudaGetLastError());
+  }
+  if (advance) {
+    adamw_advance_kernel<<<1, 1, 0, st>>>(plan->d_counter);
+    ANC_CUDA(cudaGetLastError());
+  }
+  return ANC_OK;
+}
+
 int anc_adamw_plan_destroy(anc_adamw_plan *plan) {
   if (!plan) return ANC_OK;
   anc_device_guard guard(plan->ctx->device);
   cudaStreamSynchronize(plan->ctx->stream);
+  if (plan->d_sched) cudaFree(plan->d_sched);
+  if (plan->d_counter) cudaFree(plan->d_counter);
   if (plan->d_tensors) cudaFree(plan->d_tensors);
   if (plan->d_chunks) cudaFree(plan->d_chunks);
   delete plan;

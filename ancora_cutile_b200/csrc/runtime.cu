@@ -237,6 +237,39 @@ int anc_stream_wait_event(void *stream, void *ev) {
   return ANC_OK;
 }
 
+int anc_graph_begin(anc_ctx *ctx, void *stream) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaStreamBeginCapture(anc_pick_stream(ctx, stream), cudaStreamCaptureModeThreadLocal));
+  return ANC_OK;
+}
+
+int anc_graph_end(anc_ctx *ctx, void *stream, void **graph_exec) {
+  ANC_REQUIRE(ctx && graph_exec, "NULL argument");
+  anc_device_guard g(ctx->device);
+  *graph_exec = nullptr;
+  cudaGraph_t graph = nullptr;
+  ANC_CUDA(cudaStreamEndCapture(anc_pick_stream(ctx, stream), &graph));
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return anc_cuda_fail(e, "cudaGraphInstantiate");
+  *graph_exec = (void *)exec;
+  return ANC_OK;
+}
+
+int anc_graph_launch(anc_ctx *ctx, void *graph_exec, void *stream) {
+  ANC_REQUIRE(ctx && graph_exec, "NULL argument");
+  anc_device_guard g(ctx->device);
+  ANC_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, anc_pick_stream(ctx, stream)));
+  return ANC_OK;
+}
+
+int anc_graph_destroy(void *graph_exec) {
+  if (graph_exec) ANC_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+  return ANC_OK;
+}
+
 __global__ void anc_flush_kernel(uint4 *p, size_t n16) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t stride = (size_t)gridDim.x * blockDim.x;

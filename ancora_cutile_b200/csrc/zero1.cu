@@ -15,6 +15,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*GroupStart)() = nullptr;
@@ -69,6 +70,7 @@ int anc_nccl_load(const char *path) {
             load_sym(g_nccl.CommDestroy, "ncclCommDestroy") &&
             load_sym(g_nccl.AllGather, "ncclAllGather") &&
             load_sym(g_nccl.Broadcast, "ncclBroadcast") &&
+            load_sym(g_nccl.ReduceScatter, "ncclReduceScatter") &&
             load_sym(g_nccl.AllReduce, "ncclAllReduce") &&
             load_sym(g_nccl.GroupStart, "ncclGroupStart") &&
             load_sym(g_nccl.GroupEnd, "ncclGroupEnd") &&
@@ -140,6 +142,20 @@ int anc_comm_allgather_bf16(anc_comm *c, uint16_t *arena, uint64_t elems_per_ran
   const size_t bytes = (size_t)elems_per_rank * 2;
   ANC_NCCL(g_nccl.AllGather((const char *)arena + (size_t)c->rank * bytes, arena, bytes, ncclUint8,
                             c->comm, st));
+  return ANC_OK;
+}
+
+int anc_comm_reduce_scatter_grads(anc_comm *c, void *arena, uint64_t elems_per_rank, int grad_dtype,
+                                  void *stream) {
+  ANC_REQUIRE(c && arena, "NULL argument");
+  ANC_REQUIRE(grad_dtype == ANC_GRAD_BF16 || grad_dtype == ANC_GRAD_F32, "bad grad_dtype");
+  if (elems_per_rank == 0) return ANC_OK;
+  anc_device_guard guard(c->ctx->device);
+  cudaStream_t st = anc_pick_stream(c->ctx, stream);
+  const size_t esz = grad_dtype == ANC_GRAD_BF16 ? 2 : 4;
+  const ncclDataType_t dt = grad_dtype == ANC_GRAD_BF16 ? (ncclDataType_t)9 /* ncclBfloat16 */ : ncclFloat32;
+  ANC_NCCL(g_nccl.ReduceScatter(arena, (char *)arena + (size_t)c->rank * elems_per_rank * esz,
+                                (size_t)elems_per_rank, dt, ncclSum, c->comm, st));
   return ANC_OK;
 }
 

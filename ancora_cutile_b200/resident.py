@@ -274,6 +274,65 @@ class ResidentHybrid:
         if multi:
             self.exchange(si)
 
+    def upload_full_grads(self, grads, si=None):
+        """Host -> device copy of ALL gradients (a data-parallel replica's local gradients, to
+        be summed across ranks by ``reduce_scatter_grads``)."""
+        self._stage_grads(grads)
+        pa, pm, _ = self._pin_g
+        it = self._gdt.itemsize
+        L.check(L.lib().anc_h2d(self.ctx.handle, self.a_g.ptr, pa.ptr, self.a_padded * it, si or None, 0))
+        L.check(L.lib().anc_h2d(self.ctx.handle, self.m_g.ptr, pm.ptr, self.m_total * it, si or None, 0))
+
+    def reduce_scatter_grads(self, si=None):
+        """Data-parallel gradient reduction feeding the ZeRO-1 owners: every rank holds local
+        gradients for all parameters in its gradient arenas; afterwards each rank's own AdamW
+        slice and own Muon matrices hold the sum over ranks (NCCL reduce-scatter per unit, in
+        place, in the gradient dtype).  Nothing in the reference corresponds to it (single
+        GPU); it is the producer side of the sharded step."""
+        assert self.comm is not None, "reduce_scatter_grads needs an NCCL communicator"
+        it = self._gdt.itemsize
+        self.comm.reduce_scatter_grads(self.a_g.ptr, self.a_per, self.grad_dtype, si)
+        for g in self.groups:
+            self.comm.reduce_scatter_grads(self.m_g.ptr + g["base"] * it, g["per"], self.grad_dtype, si)
+
+    # ---------------------------------------------------------------- graph replay
+    def capture_step(self, si=None, horizon=4096):
+        """Captures one whole step into a CUDA graph whose replay advances the optimizer by one
+        step: AdamW's step number and scalars come from device memory (a schedule for the next
+        ``horizon`` steps is uploaded here), everything else in the step has fixed arguments.
+        Call after at least one eager ``step`` (first calls allocate); hyper-parameters are
+        frozen into the graph; the copy-engine exchange is not capturable (its sequence numbers
+        are launch arguments), the NCCL exchange is."""
+        assert self.p2p is None, "graph replay is not available with the copy-engine exchange"
+        si = si or self.ctx.stream
+        a = self.adamw_kw
+        self.ctx.sync(si)
+        self.adamw.set_schedule(self.t + 1, horizon, a["lr"], a["betas"][0], a["betas"][1], a["eps"])
+        self._graph_limit = self.t + horizon
+        lib = L.lib()
+        L.check(lib.anc_graph_begin(self.ctx.handle, si))
+        try:
+            for u in self.units:
+                if u[0] == "adamw":
+                    u[1].step_scheduled(si, advance=True)
+                else:
+                    self._compute_unit(u, si)
+            if self.world > 1:
+                self.exchange(si)
+        finally:
+            g = C.c_void_p()
+            L.check(lib.anc_graph_end(self.ctx.handle, si, C.byref(g)))
+        if getattr(self, "_graph", None):
+            lib.anc_graph_destroy(self._graph)
+        self._graph = g
+
+    def replay_step(self, si=None):
+        """One optimizer step by replaying the captured graph (asynchronous)."""
+        assert getattr(self, "_graph", None), "capture_step first"
+        assert self.t < self._graph_limit, "schedule exhausted: capture_step again"
+        self.t += 1
+        L.check(L.lib().anc_graph_launch(self.ctx.handle, self._graph, si or self.ctx.stream))
+
     def exchange(self, si=None):
         """NCCL path: one in-place all-gather per unit."""
         assert self.comm is not None, "world > 1 needs a communicator"
@@ -474,6 +533,9 @@ class ResidentHybrid:
 
     def free(self):
         self.ctx.sync()
+        if getattr(self, "_graph", None):
+            L.lib().anc_graph_destroy(self._graph)
+            self._graph = None
         if self.p2p is not None:
             self.p2p.destroy()
             self.p2p = None

@@ -115,6 +115,11 @@ class Comm:
         L.check(L.lib().anc_comm_allgather_bf16(self.handle, arena_ptr, int(elems_per_rank),
                                                 C.c_void_p(stream or None)))
 
+    def reduce_scatter_grads(self, arena_ptr, elems_per_rank, grad_dtype="bf16", stream=None):
+        L.check(L.lib().anc_comm_reduce_scatter_grads(self.handle, arena_ptr, int(elems_per_rank),
+                                                      L.GRAD_BF16 if grad_dtype == "bf16" else L.GRAD_F32,
+                                                      C.c_void_p(stream or None)))
+
     def barrier(self, stream=None):
         L.check(L.lib().anc_comm_barrier(self.handle, C.c_void_p(stream or None)))
 

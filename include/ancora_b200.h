@@ -88,6 +88,12 @@ ANC_API int anc_event_record(void *ev, void *stream);
 ANC_API int anc_event_sync(void *ev);
 ANC_API int anc_event_elapsed_ms(void *start, void *stop, float *ms);
 ANC_API int anc_event_destroy(void *ev);
+/* Stream capture into an executable CUDA graph and its replay (thread-local capture mode).
+ * Run the work once eagerly first: first calls allocate tables and set kernel attributes. */
+ANC_API int anc_graph_begin(anc_ctx *ctx, void *stream);
+ANC_API int anc_graph_end(anc_ctx *ctx, void *stream, void **graph_exec);
+ANC_API int anc_graph_launch(anc_ctx *ctx, void *graph_exec, void *stream);
+ANC_API int anc_graph_destroy(void *graph_exec);
 /* Extra streams for overlapping copies / collectives with compute. */
 ANC_API int anc_stream_create(anc_ctx *ctx, void **stream);
 ANC_API int anc_stream_destroy(anc_ctx *ctx, void *stream);
@@ -135,6 +141,19 @@ ANC_API int anc_adamw_plan_total(anc_adamw_plan *plan, uint64_t *arena_elems, ui
  * ancora/optim/adamw.py:23-41.  seed/step key the Philox stream (ANC_ROUND_SR). */
 ANC_API int anc_adamw_step(anc_adamw_plan *plan, const anc_adamw_scalars *s, int rounding,
                            uint64_t seed, uint64_t step, void *stream);
+/* Replayable form: the step number and the per-step scalars live in device memory, so the
+ * same launch can be replayed from a CUDA graph.  The reference keeps its optimizer step
+ * out of its captured graph because the bias corrections are kernel arguments that change
+ * every step (ancora/model/resident_prefix_model.py:157-161).  table[k] holds the scalars
+ * of step first_step + k (built by the host with the same float32 definitions as
+ * anc_adamw_step); the device counter starts at first_step.  anc_adamw_step_scheduled uses
+ * table[counter - first_step] and the counter as the SR step; advance != 0 appends a
+ * one-thread kernel that increments the counter (give it on the last AdamW launch of a
+ * step).  A counter outside the table sets status bit 0x8 and the launch does nothing. */
+ANC_API int anc_adamw_plan_set_schedule(anc_adamw_plan *plan, const anc_adamw_scalars *table, int n,
+                                        uint64_t first_step);
+ANC_API int anc_adamw_step_scheduled(anc_adamw_plan *plan, int rounding, uint64_t seed, int advance,
+                                     void *stream);
 ANC_API int anc_adamw_plan_destroy(anc_adamw_plan *plan);
 
 /* ------------------------------------------------------------------- Muon ---- */
@@ -282,6 +301,12 @@ ANC_API int anc_comm_destroy(anc_comm *comm);
  * [r*elems_per_rank, (r+1)*elems_per_rank) of `arena` (bf16 elements). */
 ANC_API int anc_comm_allgather_bf16(anc_comm *comm, uint16_t *arena, uint64_t elems_per_rank,
                                     void *stream);
+/* In-place sum reduce-scatter of a gradient arena made of `world` equal contiguous slices
+ * (bf16 or f32 elements): afterwards rank r's slice holds the sum over all ranks of that
+ * slice (the other slices are unspecified).  Feeds the ZeRO-1 owner of each slice from
+ * data-parallel replicas. */
+ANC_API int anc_comm_reduce_scatter_grads(anc_comm *comm, void *arena, uint64_t elems_per_rank,
+                                          int grad_dtype, void *stream);
 /* Grouped broadcasts of variable segments: segment i (ptr[i], elems[i]) is sent
  * by root[i] to everybody. */
 ANC_API int anc_comm_bcast_segments(anc_comm *comm, uint16_t *const *ptr, const uint64_t *elems,

@@ -166,3 +166,31 @@ def test_state_dict_resume_is_bit_exact(ctx):
         sd2 = dict(sd); sd2["world"] = 2
         b.load_state_dict(sd2)
     b.free()
+
+
+def test_graph_replay_equals_eager_steps(ctx):
+    """One captured step replayed three times = three eager steps, bit for bit (the AdamW step
+    number, bias corrections and SR stream advance inside the graph)."""
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=12)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    g = S.synthetic_grads_bf16(shp, seed=13)
+    res = []
+    for mode in ("eager", "graph"):
+        eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=5,
+                                 schedule=anc.PE_SCHEDULE, ctx=ctx)
+        eng.upload_grads(g, ctx.stream)
+        eng.step(ctx.stream)
+        if mode == "graph":
+            eng.capture_step(ctx.stream, horizon=8)
+        for _ in range(3):
+            eng.replay_step(ctx.stream) if mode == "graph" else eng.step(ctx.stream)
+        ctx.sync()
+        assert ctx.status() == 0 and eng.t == 4
+        bits, _ = eng.download_weights_bits()
+        res.append(({n: b.copy() for n, b in bits.items()}, eng.master()))
+        eng.free()
+    for n in shp:
+        assert np.array_equal(res[0][0][n], res[1][0][n]), n
+        assert np.array_equal(res[0][1][n][2], res[1][1][n][2]), n

@@ -104,3 +104,78 @@ def test_two_ranks_hold_the_single_gpu_bits(mode):
         assert status == 0, (rank, status)
         for n, w in want.items():
             assert bits[n] == w.tobytes(), (mode, rank, n)
+
+
+def _rs_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    import ancora_cutile_b200 as anc
+    from ancora_cutile_b200 import shapes as S
+    from ancora_cutile_b200.zero1 import Comm, nccl_unique_id
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    anc.set_device(rank)
+    ctx = anc.get_context()
+    box = [nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    comm = Comm(ctx, box[0], rank, world)
+    shp = _small()
+    params = S.synthetic_params(shp, seed=11)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=3,
+                             rank=rank, world=world, comm=comm, schedule=anc.PE_SCHEDULE, ctx=ctx)
+    eng.upload_full_grads(S.synthetic_grads_bf16(shp, seed=40 + rank), ctx.stream)     # rank-local gradients
+    eng.reduce_scatter_grads(ctx.stream)
+    ctx.sync()
+    owned = {}
+    for n in shp:
+        s, e = eng.owned_range(n)
+        if e > s:
+            owned[n] = (s, e, eng.grad_view(n).to_numpy().reshape(-1)[s:e].tobytes())
+    eng.step(ctx.stream)
+    ctx.sync()
+    bits, _ = eng.download_weights_bits()
+    q.put((rank, ctx.status(), owned, {n: b.tobytes() for n, b in bits.items()}))
+    dist.barrier()
+    eng.free()
+    comm.destroy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_grad_reduce_scatter_feeds_the_sharded_step():
+    """Two data-parallel replicas with different local gradients: after the reduce-scatter every
+    owner holds bf16(g0 + g1) of its share (within one bf16 ulp: NCCL adds in its own precision),
+    and the sharded step on those gradients leaves both ranks with identical parameters."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from ancora_cutile_b200 import shapes as S
+    from ancora_cutile_b200.bf16 import bits_to_f32, f32_to_bf16_bits
+    shp = _small()
+    g0, g1 = S.synthetic_grads_bf16(shp, seed=40), S.synthetic_grads_bf16(shp, seed=41)
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = 29700 + (os.getpid() % 1000)
+    procs = [mpc.Process(target=_rs_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted([q.get(timeout=300) for _ in range(2)], key=lambda x: x[0])
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    covered = {n: 0 for n in shp}
+    for rank, status, owned, bits in got:
+        assert status == 0
+        for n, (s, e, raw) in owned.items():
+            have = np.frombuffer(raw, np.uint16)
+            want = f32_to_bf16_bits(bits_to_f32(g0[n]).reshape(-1)[s:e] + bits_to_f32(g1[n]).reshape(-1)[s:e])
+            assert np.abs(have.astype(np.int32) - want.astype(np.int32)).max() <= 1, (rank, n)
+            assert np.mean(have != want) < 1e-3, (rank, n)
+            covered[n] += e - s
+    for n, s in shp.items():
+        assert covered[n] == int(np.prod(s)), n
+    for n in shp:
+        assert got[0][3][n] == got[1][3][n], n              # both ranks end with the same parameters
