@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <map>
+#include <mutex>
 #include <stdlib.h>
 #include <vector>
 #include "anc_internal.h"
@@ -754,10 +755,12 @@ struct GemmCache {
   bool attr2_set = false;
 };
 std::map<anc_ctx *, GemmCache *> g_caches;
+std::mutex g_caches_mu;   // contexts of different threads may launch concurrently
 
 // Tile list of one matrix.  sym: lower-triangular 128-blocks of an (mb x mb) grid packed
 // into 256-wide tiles; else the full (mb x nb) grid.
 int get_tile_tab(anc_ctx *ctx, bool sym, bool pair, int mb, int nb, TileTab *out) {
+  std::lock_guard<std::mutex> lock(g_caches_mu);
   GemmCache *&gc = g_caches[ctx];
   if (!gc) gc = new GemmCache();
   const uint64_t key = ((uint64_t)(sym ? 1 : 0) << 40) | ((uint64_t)(pair ? 1 : 0) << 41) |
@@ -798,6 +801,7 @@ int get_tile_tab(anc_ctx *ctx, bool sym, bool pair, int mb, int nb, TileTab *out
 }  // namespace
 
 void anc_gemm_cache_destroy(anc_ctx *ctx) {
+  std::lock_guard<std::mutex> lock(g_caches_mu);
   auto it = g_caches.find(ctx);
   if (it == g_caches.end()) return;
   for (auto &kv : it->second->tabs) cudaFree(kv.second.d_tab);
@@ -833,7 +837,11 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
   TileTab tt;
   rc = get_tile_tab(ctx, mode != 2, pair, mb, mode == 2 ? N / 128 : mb, &tt);
   if (rc) return rc;
-  GemmCache *gc = g_caches[ctx];
+  GemmCache *gc;
+  {
+    std::lock_guard<std::mutex> lock(g_caches_mu);
+    gc = g_caches[ctx];
+  }
   if (!gc->attr_set) {
     ANC_CUDA(cudaFuncSetAttribute(ns_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemBytes));
