@@ -251,16 +251,22 @@ def main():
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)
     eng.upload_grads(pin, ctx.stream)
-    # optimizer state as BASELINE configs describe: m ~ N(0,1e-4), v = |N(0,1e-6)|, momentum ~ N(0,1e-3)
-    rng = np.random.default_rng(2 + rank)
-    for buf, std, absval in ((eng.a_m, 1e-4, False), (eng.a_v, 1e-6, True), (eng.m_buf, 1e-3, False)):
-        n = buf.shape[0]
-        blk = rng.standard_normal(min(n, 1 << 24), dtype=np.float32) * np.float32(std)
-        if absval:
-            blk = np.abs(blk)
-        for o in range(0, n, blk.size):
-            k = min(blk.size, n - o)
-            buf.slice_elems(o, k).upload(blk[:k])
+    # optimizer state as BASELINE configs describe: m ~ N(0,1e-4), v = |N(0,1e-6)|, momentum ~ N(0,1e-3).
+    # Each tensor's state comes from its own seeded stream and only the range this rank owns is
+    # uploaded, so the state (and therefore the result) does not depend on the number of ranks.
+    names = list(shp)
+    for idx, name in enumerate(names):
+        lo, hi = eng.owned_range(name)
+        if hi <= lo:
+            continue
+        n = int(np.prod(shp[name]))
+        r = np.random.default_rng(1000 + idx)
+        if name in eng.a_off:
+            o = eng.a_off[name] + lo - eng.a_begin
+            eng.a_m.slice_elems(o, hi - lo).upload((r.standard_normal(n, dtype=np.float32) * np.float32(1e-4))[lo:hi])
+            eng.a_v.slice_elems(o, hi - lo).upload(np.abs(r.standard_normal(n, dtype=np.float32) * np.float32(1e-6))[lo:hi])
+        else:
+            eng.m_buf.slice_elems(eng.m_own_off[name], n).upload(r.standard_normal(n, dtype=np.float32) * np.float32(1e-3))
     ctx.sync()
 
     if eng.muon is not None:
