@@ -39,8 +39,10 @@ class ResidentHybrid:
                  grad_dtype="bf16", rounding="sr", seed=0, rank=0, world=1, comm=None, p2p=None,
                  schedule=_UNSET, max_batch=0, ctx=None):
         """params: {name: fp32 ndarray} (every rank passes the same dict).
-        comm: zero1.Comm (NCCL all-gather after the step).  p2p: True to prepare the
-        copy-engine exchange (finish with ``connect_p2p``), which overlaps with compute."""
+        comm: zero1.Comm; the updated bf16 parameters are exchanged with one NCCL all-gather per
+        unit, issued on a second stream as soon as the unit is computed (``nccl_overlap``; set it
+        to False for plain all-gathers after the step).  p2p: True to prepare the experimental
+        copy-engine exchange instead (finish with ``connect_p2p``)."""
         self.ctx = ctx or get_context()
         self.rank, self.world, self.comm = int(rank), int(world), comm
         self.grad_dtype, self.rounding, self.seed = grad_dtype, rounding, int(seed)
@@ -50,6 +52,7 @@ class ResidentHybrid:
         self.muon_kw.update(muon_kw or {})
         self._sched = schedule
         self.t = 0
+        self.nccl_overlap = comm is not None
         gdt = np.uint16 if grad_dtype == "bf16" else np.float32
         self._gdt = np.dtype(gdt)
         mset = set(muon_names)
@@ -154,6 +157,7 @@ class ResidentHybrid:
         self._pin_g = None
         self._pin_w = None
         self._streams = None
+        self._comm_stream = None
         self.p2p = None
         if p2p and W > 1:
             from .zero1 import P2PExchange
@@ -268,6 +272,28 @@ class ResidentHybrid:
                 arena, off, n = self.unit_span(u)
                 self.p2p.push(arena, off * 2, n * 2, ev)
             self.p2p.finish(si)
+            return
+        if multi and self.nccl_overlap:
+            # NCCL all-gather of each unit on a second stream as soon as the unit is computed
+            if self._comm_stream is None:
+                st = C.c_void_p()
+                L.check(L.lib().anc_stream_create(self.ctx.handle, C.byref(st)))
+                self._comm_stream = st.value
+            cs = self._comm_stream
+            evs = self._events(len(self.units) + 1)
+            lib = L.lib()
+            for u, ev in zip(self.units, evs):
+                self._compute_unit(u, si)
+                ev.record(si)
+                L.check(lib.anc_stream_wait_event(cs, ev.handle))
+                if u[0] == "adamw":
+                    self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, cs)
+                else:
+                    g = self._gmap[u[4]]
+                    self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], cs)
+            done = evs[len(self.units)]
+            done.record(cs)
+            L.check(lib.anc_stream_wait_event(si, done.handle))
             return
         for u in self.units:
             self._compute_unit(u, si)
@@ -557,6 +583,9 @@ class ResidentHybrid:
             for s in self._streams:
                 L.lib().anc_stream_destroy(self.ctx.handle, s)
             self._streams = None
+        if self._comm_stream:
+            L.lib().anc_stream_destroy(self.ctx.handle, self._comm_stream)
+            self._comm_stream = None
         for e in getattr(self, "_evpool", []):
             e.destroy()
         self._evpool = []

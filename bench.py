@@ -166,6 +166,7 @@ def main():
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "moe"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--dump-digests", default=None, help="write a per-tensor fingerprint map to this file (rank 0)")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: fewer layers")
     ap.add_argument("--vocab", type=int, default=None, help="profiling only: smaller vocabulary")
     args = ap.parse_args()
@@ -236,17 +237,22 @@ def main():
     anc.set_polar_express(True)
     params = S.synthetic_params(shp, seed=0)
     no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
-    use_p2p = world > 1 and os.environ.get("ANCORA_EXCHANGE", "p2p") == "p2p"
+    # exchange of the updated bf16 parameters: "nccl_overlap" (default), "nccl" (after the step),
+    # "p2p" (experimental copy-engine pushes)
+    xmode = os.environ.get("ANCORA_EXCHANGE", "nccl_overlap")
+    use_p2p = world > 1 and xmode == "p2p"
     eng = anc.ResidentHybrid(params, muon_names, no_decay_names=no_decay, adamw_kw=ADAMW_KW, muon_kw=MUON_KW,
                              grad_dtype="bf16", rounding="sr", seed=SEED_SR, rank=rank, world=world,
                              comm=comm, p2p=use_p2p, schedule=anc.PE_SCHEDULE, ctx=ctx)
     del params
+    eng.nccl_overlap = world > 1 and xmode == "nccl_overlap"
     if use_p2p:
         box = [None] * world
         dist.all_gather_object(box, eng.p2p_handles())
         eng.connect_p2p(box)
     config["exchange"] = ("copy-engine pushes over NVLink (IPC), overlapped per unit" if use_p2p
-                          else ("NCCL all-gather" if world > 1 else "none"))
+                          else ("NCCL all-gather per unit on a second stream" if eng.nccl_overlap
+                                else ("NCCL all-gather after the step" if world > 1 else "none")))
     # synthetic bf16 gradients, written into the page-locked staging views and uploaded once
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)
@@ -371,6 +377,11 @@ def main():
     for name in shp:
         hsh.update(np.ascontiguousarray(bits[name]).tobytes())
     digest = hsh.hexdigest()
+    if args.dump_digests and rank == 0:
+        per = {name: hashlib.blake2b(np.ascontiguousarray(bits[name]).tobytes(), digest_size=8).hexdigest()
+               for name in shp}
+        with open(args.dump_digests, "w") as f:
+            json.dump({"world": world, "owner": {n: eng.m_owner.get(n, -1) for n in shp}, "digests": per}, f)
     if dist is not None:
         box = [None] * world
         dist.all_gather_object(box, digest)
