@@ -257,7 +257,7 @@ def main():
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)
     eng.upload_grads(pin, ctx.stream)
-    # optimizer state as BASELINE configs describe: m ~ N(0,1e-4), v = |N(0,1e-6)|, momentum ~ N(0,1e-3).
+    # synthetic optimizer state: m ~ N(0,1e-4), v = |N(0,1e-6)|, momentum ~ N(0,1e-3).
     # Each tensor's state comes from its own seeded stream and only the range this rank owns is
     # uploaded, so the state (and therefore the result) does not depend on the number of ranks.
     names = list(shp)

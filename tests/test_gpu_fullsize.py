@@ -1,8 +1,8 @@
-"""GPU: BASELINE configurations at their full sizes.
+"""GPU: the benchmark configurations at their full sizes.
 
-config 1: AdamW on one 151936x1024 tensor, bf16 grads, step 10, SR seed 1234 -- the device
+AdamW case: AdamW on one 151936x1024 tensor, bf16 grads, step 10, SR seed 1234 -- the device
 result must equal the oracle bit for bit on all 155,582,464 elements (fp32 state and bf16 copy).
-config 5 shape: a batch of 16 rectangular experts (768x1024) through the whole Muon step, each
+MoE expert shape: a batch of 16 rectangular experts (768x1024) through the whole Muon step, each
 compared with its own fp32 host result, plus the size-independent property that the bf16
 Newton-Schulz output is close to orthogonal."""
 import numpy as np

@@ -1,7 +1,7 @@
 """GPU (needs >= 2 GPUs, skipped otherwise): the ZeRO-1 step on two real ranks, one process per
 GPU, with both exchange paths.  After the step every rank must hold, for every parameter, exactly
-the bf16 bits the single-GPU engine produces (BASELINE config 4: "bitwise identical to the 1-GPU
-result").  Ranks are plain child processes; the NCCL id and the IPC handles travel through gloo."""
+the bf16 bits the single-GPU engine produces (the sharded step must be bitwise identical to the 1-GPU
+result).  Ranks are plain child processes; the NCCL id and the IPC handles travel through gloo."""
 import ctypes as C
 import os
 import sys
