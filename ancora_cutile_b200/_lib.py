@@ -33,7 +33,8 @@ class AdamWScalars(C.Structure):
 
 
 class MuonOutputs(C.Structure):
-    _fields_ = [("fp8", C.c_void_p), ("fp8_scale", C.c_void_p), ("p16_t", C.c_void_p)]
+    _fields_ = [("fp8", C.c_void_p), ("fp8_scale", C.c_void_p), ("p16_t", C.c_void_p),
+                ("fp8_t", C.c_void_p), ("fp8_scale_t", C.c_void_p)]
 
 
 class MuonWeight(C.Structure):
@@ -98,6 +99,7 @@ SIGNATURES = {
     "anc_muon_update": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "anc_fro_normalize": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "anc_fro_normalize_static": (_i, [_i, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "anc_grad_accumulate": (_i, [_vp, _vp, _vp, _i, _vp, _u64, _u64, _f, _i, _u64, _u64, _i, _vp]),
     "anc_nccl_load": (_i, [C.c_char_p]),
     "anc_nccl_unique_id": (_i, [_vp]),
     "anc_comm_create": (_i, [_vp, _vp, _i, _i, _pp]),

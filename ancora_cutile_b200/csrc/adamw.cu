@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <vector>
 #include "anc_internal.h"
+#include "philox.cuh"
 
 namespace {
 
@@ -43,21 +44,6 @@ struct Scalars {
   float b1, omb1, b2, omb2, eps, lr, ibc1, ibc2;
 };
 
-__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-    const uint32_t n0 = hi1 ^ c1 ^ k0;
-    const uint32_t n2 = hi0 ^ c3 ^ k1;
-    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
-  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
-}
-
 __device__ __forceinline__ void adamw_elem(float g, float &p, float &m, float &v, float wd,
                                            const Scalars &s) {
   const float mn = __fadd_rn(__fmul_rn(s.b1, m), __fmul_rn(s.omb1, g));
@@ -68,15 +54,6 @@ __device__ __forceinline__ void adamw_elem(float g, float &p, float &m, float &v
   p = __fsub_rn(p, __fmul_rn(s.lr, upd));
   m = mn;
   v = vn;
-}
-
-__device__ __forceinline__ uint32_t bf16_rne(float x) {
-  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
-}
-
-__device__ __forceinline__ uint32_t bf16_sr(float x, uint32_t dither16) {
-  const uint32_t u = __float_as_uint(x);
-  return (x != x) ? 0x7FFFu : ((u + dither16) >> 16);
 }
 
 template <bool kGradF32>

@@ -22,7 +22,7 @@ struct anc_ctx {
 // entries of the device tables the Muon plan builds for the group launches
 struct anc_mom_entry { float *buf; const void *g; int K, N, tr, _pad; };
 struct anc_upd_entry { float *p32; uint16_t *p16; int K, N, tr, _pad; };
-struct anc_upd_extra { uint8_t *fp8; uint8_t *scale; uint16_t *p16_t; int64_t _pad; };
+struct anc_upd_extra { uint8_t *fp8; uint8_t *scale; uint16_t *p16_t; uint8_t *fp8_t; uint8_t *scale_t; int64_t _pad; };
 
 // device status bits
 #define ANC_DEV_TIMEOUT_TMA 0x1u     // producer/consumer mbarrier wait ran out

@@ -251,12 +251,17 @@ update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, in
 //                 (ancora/kernels/quant.py:56-68 `_quant_mxfp8_w`; layout (K,N) u8 + (K/32,N) u8)
 //   p16_t       : the transposed bf16 copy (N,K) a backward pass reads
 //                 (ancora/kernels/moe.py:371-377 `_transpose_e`)
+//   fp8_t + scale_t : the same MXFP8 bytes in the transposed layout a column-major B operand
+//                 wants, (N,K) u8 + (N,K/32) u8 (ancora/kernels/quant.py:79-90 `_quant_mxfp8_w_cm`)
 struct UpdX {
   uint8_t *fp8;
   uint8_t *scale;
   uint16_t *p16_t;
+  uint8_t *fp8_t;
+  uint8_t *scale_t;
   int64_t _pad;
 };
+constexpr int kQPad = 16;   // row pad of the byte staging tile (keeps rows 16-byte aligned)
 
 __device__ __forceinline__ uint32_t e4m3_rn(float x) {
   // cvt.rn.satfinite.e4m3x2.f32 packs two values; the high one is zero here
@@ -270,8 +275,9 @@ __device__ __forceinline__ uint32_t e4m3_rn(float x) {
 __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x, int slot,
                                                    const uint16_t *obase, float lr_scale, int ti, int tj,
                                                    uint16_t (*sm)[kTile + kPad], uint32_t (*wmax)[2][kTile],
-                                                   uint8_t (*sbyte)[kTile]) {
+                                                   uint8_t (*sbyte)[kTile], uint8_t (*sq)[kTile + kQPad]) {
   const uint16_t *wo = obase + (size_t)slot * w.K * w.N;
+  const bool want_q = x.fp8 != nullptr || x.fp8_t != nullptr;
   const int c8 = (threadIdx.x & 7) * 8;
   const int r0 = threadIdx.x >> 3;
   const int col = tj * kTile + c8;
@@ -324,7 +330,7 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
           make_uint4(h[k][0] | (h[k][1] << 16), h[k][2] | (h[k][3] << 16), h[k][4] | (h[k][5] << 16),
                      h[k][6] | (h[k][7] << 16));
   }
-  if (x.fp8) {
+  if (want_q) {
     // column maxima of |w| per 32-row block: 4 rows per warp by shuffles, 8 warps through smem
 #pragma unroll
     for (int k = 0; k < 2; ++k)
@@ -337,7 +343,7 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
       }
   }
   __syncthreads();
-  if (x.fp8 && threadIdx.x < 2 * kTile) {
+  if (want_q && threadIdx.x < 2 * kTile) {
     const int k = threadIdx.x >> 6, c = threadIdx.x & 63;
     uint32_t a = wmax[0][k][c];
 #pragma unroll
@@ -345,7 +351,8 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
     const uint32_t ea = (a >> 7) & 0xFF;                // exponent field of the bf16 = of the float
     const uint32_t byte = ea >= 7 ? ea - 7 : 0;
     sbyte[k][c] = (uint8_t)byte;
-    x.scale[((size_t)(ti * 2 + k)) * w.N + (size_t)tj * kTile + c] = (uint8_t)byte;
+    if (x.fp8) x.scale[((size_t)(ti * 2 + k)) * w.N + (size_t)tj * kTile + c] = (uint8_t)byte;
+    if (x.fp8_t) x.scale_t[((size_t)tj * kTile + c) * (size_t)(w.K / 32) + (size_t)(ti * 2 + k)] = (uint8_t)byte;
   }
   if (x.p16_t) {
     // transposed store of the bf16 tile: thread handles output row t/4, 16 elements
@@ -360,7 +367,7 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
     reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
   }
   __syncthreads();
-  if (x.fp8) {
+  if (want_q) {
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       uint32_t q[8];
@@ -370,10 +377,28 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
         const float inv = __uint_as_float((254u - byte) << 23);      // 2^(127 - byte), exact
         q[j] = e4m3_rn(__fmul_rn(bf16_f32(h[k][j]), inv));
       }
-      const size_t idx = (size_t)(ti * kTile + r0 + 32 * k) * w.N + col;
-      *reinterpret_cast<uint2 *>(x.fp8 + idx) =
+      const uint2 packed =
           make_uint2(q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24), q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24));
+      if (x.fp8) {
+        const size_t idx = (size_t)(ti * kTile + r0 + 32 * k) * w.N + col;
+        *reinterpret_cast<uint2 *>(x.fp8 + idx) = packed;
+      }
+      if (x.fp8_t) *reinterpret_cast<uint2 *>(&sq[r0 + 32 * k][c8]) = packed;
     }
+  }
+  if (x.fp8_t) {
+    // transposed store of the byte tile: thread handles output row t/4 (a column of the weight),
+    // 16 consecutive K positions
+    __syncthreads();
+    const int oc = threadIdx.x >> 2;
+    const int rr = (threadIdx.x & 3) * 16;
+    uint32_t pk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      pk[j] = (uint32_t)sq[rr + 4 * j][oc] | ((uint32_t)sq[rr + 4 * j + 1][oc] << 8) |
+              ((uint32_t)sq[rr + 4 * j + 2][oc] << 16) | ((uint32_t)sq[rr + 4 * j + 3][oc] << 24);
+    uint8_t *dst = x.fp8_t + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
   }
   __syncthreads();
 }
@@ -384,6 +409,7 @@ update_extras_kernel(const UpdW *__restrict__ table, const UpdX *__restrict__ ex
   __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
   __shared__ uint32_t wmax[kThreads / 32][2][kTile];
   __shared__ uint8_t sbyte[2][kTile];
+  __shared__ __align__(16) uint8_t sq[kTile][kTile + kQPad];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int total = n_w * tiles_per_w;
@@ -393,7 +419,7 @@ update_extras_kernel(const UpdW *__restrict__ table, const UpdX *__restrict__ ex
     const UpdW w = table[wi];
     const UpdX x = extras[wi];
     const int tn = w.N / kTile;
-    update_tile_extras(w, x, wi, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm, wmax, sbyte);
+    update_tile_extras(w, x, wi, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm, wmax, sbyte, sq);
   }
 }
 

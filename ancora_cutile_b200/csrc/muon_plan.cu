@@ -128,10 +128,15 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     }
     pl->groups[it->second].widx.push_back((int)pl->weights.size());
     pl->weights.push_back(w);
-    anc_muon_outputs o = {nullptr, nullptr, nullptr};
+    anc_muon_outputs o = {nullptr, nullptr, nullptr, nullptr, nullptr};
     if (outputs) o = outputs[i];
-    if ((o.fp8 == nullptr) != (o.fp8_scale == nullptr)) {
-      anc_set_error("Muon weight %d: fp8 and fp8_scale must be given together", i);
+    if ((o.fp8 == nullptr) != (o.fp8_scale == nullptr) || (o.fp8_t == nullptr) != (o.fp8_scale_t == nullptr)) {
+      anc_set_error("Muon weight %d: an fp8 output and its scale output must be given together", i);
+      plan_free(pl);
+      return ANC_E_INVALID;
+    }
+    if (((uintptr_t)o.fp8 & 7) || ((uintptr_t)o.fp8_t & 15) || ((uintptr_t)o.p16_t & 15)) {
+      anc_set_error("Muon weight %d: fp8 needs 8-byte, fp8_t and p16_t 16-byte alignment", i);
       plan_free(pl);
       return ANC_E_INVALID;
     }
@@ -153,8 +158,8 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
       mom.push_back({w.buf, w.g, w.K, w.N, w.K > w.N ? 1 : 0, 0});
       upd.push_back({w.p32, w.p16, w.K, w.N, w.K > w.N ? 1 : 0, 0});
       const anc_muon_outputs &o = pl->outputs[g.widx[s]];
-      ext.push_back({o.fp8, o.fp8_scale, o.p16_t, 0});
-      any_ext = any_ext || o.fp8 || o.p16_t;
+      ext.push_back({o.fp8, o.fp8_scale, o.p16_t, o.fp8_t, o.fp8_scale_t, 0});
+      any_ext = any_ext || o.fp8 || o.p16_t || o.fp8_t;
     }
     if (any_ext) {
       cudaError_t ee = cudaMalloc((void **)&g.d_ext, ext.size() * sizeof(anc_upd_extra));

@@ -50,3 +50,18 @@ def ns_batched(X, A, B, Y, recip, E, M, N, steps, coeffs, eps=1e-7, stream=None,
     L.check(L.lib().anc_ns_batched(ctx.handle, dev_ptr(X), dev_ptr(A), dev_ptr(B), dev_ptr(Y),
                                    dev_ptr(recip), int(E), int(M), int(N), int(steps),
                                    _coeff_array(coeffs), float(eps), C.c_void_p(stream or None)))
+
+
+def grad_accumulate(acc, src=None, g16=None, numel=None, src_dtype="f32", elem_offset=0, scale=1.0,
+                    rounding="rne", seed=0, step=0, zero_after=False, stream=None, ctx=None):
+    """acc = src + acc (float32; src f32 or bf16, optional) and, in the same sweep,
+    g16 = bf16(acc * scale) (optional; "rne" or "sr"), then acc = 0 when ``zero_after``.
+    The accumulate sweep and the downcast the reference runs separately
+    (ancora/kernels/fused.py:242-249, 144-161)."""
+    ctx = ctx or get_context()
+    if numel is None:
+        numel = int(np.prod(acc.shape))
+    L.check(L.lib().anc_grad_accumulate(ctx.handle, dev_ptr(acc), dev_ptr(src), _GRAD[src_dtype], dev_ptr(g16),
+                                        int(numel), int(elem_offset), float(np.float32(scale)),
+                                        {"rne": L.ROUND_RNE, "sr": L.ROUND_SR}[rounding], int(seed), int(step),
+                                        int(bool(zero_after)), C.c_void_p(stream or None)))

@@ -39,8 +39,10 @@ class MuonPlan:
             _check_aligned(w["K"], w["N"])
             arr[i] = L.MuonWeight(dev_ptr(w["buf"]), dev_ptr(w["G"]), dev_ptr(w["p32"]), dev_ptr(w["p16"]),
                                   int(w["K"]), int(w["N"]), int(w.get("owner", -1)), 0)
-            # optional fused post-step outputs: MXFP8 re-quant (fp8 + fp8_scale), transposed bf16 copy
-            outs[i] = L.MuonOutputs(dev_ptr(w.get("fp8")), dev_ptr(w.get("fp8_scale")), dev_ptr(w.get("p16_t")))
+            # optional fused post-step outputs: MXFP8 re-quant (fp8 + fp8_scale), transposed bf16 copy,
+            # MXFP8 in the transposed (N,K) layout (fp8_t + fp8_scale_t)
+            outs[i] = L.MuonOutputs(dev_ptr(w.get("fp8")), dev_ptr(w.get("fp8_scale")), dev_ptr(w.get("p16_t")),
+                                    dev_ptr(w.get("fp8_t")), dev_ptr(w.get("fp8_scale_t")))
         h = C.c_void_p()
         L.check(L.lib().anc_muon_plan_create_ex(self.ctx.handle, arr, outs, len(weights), _GRAD[grad_dtype],
                                                 int(my_rank), int(max_batch or 0), C.byref(h)))

@@ -186,11 +186,17 @@ ANC_API int anc_muon_plan_create(anc_ctx *ctx, const anc_muon_weight *weights, i
  * 354-357) and the transposed expert weights for the backward (kernels/moe.py:371-377,593-596).
  *   fp8       (K,N) u8  E4M3 values, quantisation blocks of 32 along K
  *   fp8_scale (K/32,N) u8  E8M0 bytes: max(exponent(max|w| of the block) - 7, 0)
- *   p16_t     (N,K) bf16  transposed copy of p16 */
+ *   p16_t     (N,K) bf16  transposed copy of p16
+ *   fp8_t, fp8_scale_t  the same MXFP8 bytes transposed, (N,K) u8 + (N,K/32) u8, the layout of
+ *             _quant_mxfp8_w_cm (ancora/kernels/quant.py:79-90) for a column-major B operand
+ * fp8 needs 8-byte alignment, fp8_t and p16_t 16-byte; a values pointer and its scale pointer
+ * are given together. */
 typedef struct anc_muon_outputs {
   uint8_t *fp8;
   uint8_t *fp8_scale;
   uint16_t *p16_t;
+  uint8_t *fp8_t;
+  uint8_t *fp8_scale_t;
 } anc_muon_outputs;
 ANC_API int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights,
                                     const anc_muon_outputs *outputs, int n_weights, int grad_dtype,
@@ -288,6 +294,23 @@ ANC_API int anc_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, in
  * legacy default stream). */
 ANC_API int anc_fro_normalize_static(int device, uint16_t *X, float *recip, int E, int M, int N,
                                      float eps, void *stream);
+
+/* --------------------------------------------------------- gradient producer ---- */
+/* One sweep that feeds the step its bf16 gradient:
+ *   acc[i] = src[i] + acc[i]        (when src != NULL; one float32 add, the `_acc_f32` sweep of
+ *                                    ancora/kernels/fused.py:242-249; src is f32 or bf16)
+ *   g16[i] = bf16(acc[i] * scale)   (when g16 != NULL; ANC_ROUND_RNE, or ANC_ROUND_SR = the bit
+ *                                    rule (bits + dither16) >> 16 of fused.py:159-161 that the
+ *                                    reference applies in `_gemm_dx_sr`, dither from
+ *                                    Philox4x32-10 keyed by (seed, step, (elem_offset + i) / 8))
+ *   acc[i] = 0                      (when zero_after != 0: ready for the next accumulation)
+ * The reference runs accumulation and downcast as separate sweeps.  `scale` is applied to
+ * the bf16 output only (1/micro-batches, 1/world), never stored in acc.  elem_offset is the
+ * global index of element 0, so a sharded arena draws the same bits as an unsharded one.
+ * Use a seed different from the AdamW step's: both streams share the counter layout. */
+ANC_API int anc_grad_accumulate(anc_ctx *ctx, float *acc, const void *src, int src_dtype, uint16_t *g16,
+                                uint64_t numel, uint64_t elem_offset, float scale, int round_mode,
+                                uint64_t seed, uint64_t step, int zero_after, void *stream);
 
 /* ----------------------------------------------------------------- ZeRO-1 ---- */
 /* No counterpart in the reference (single GPU, ancora README.md:93).  NCCL is

@@ -58,6 +58,13 @@ def quant_mxfp8_w(w16):
     return q, byte
 
 
+def quant_mxfp8_w_cm(w16):
+    """w16: (K,N) bf16 bits -> (fp8 (N,K) uint8, scale (N,K//32) uint8): the same bytes as
+    `quant_mxfp8_w`, stored transposed (ancora/kernels/quant.py:79-90, `_quant_mxfp8_w_cm`)."""
+    q, byte = quant_mxfp8_w(w16)
+    return np.ascontiguousarray(q.T), np.ascontiguousarray(byte.T)
+
+
 def dequant_mxfp8_w(q, byte):
     K, N = q.shape
     v = e4m3_table()[q].reshape(K // 32, 32, N)
