@@ -350,6 +350,30 @@ def main():
         "state_bytes_per_gpu": eng.state_bytes() + (eng.muon.scratch_bytes() if eng.muon else 0),
     }
 
+    # ---- gradient producer (accumulate + SR downcast in one sweep) on an arena of the AdamW slice's
+    # size, timed alone after the step loop: float32 accumulator, bf16 contribution, bf16 output ----
+    if a_owned > 0:
+        from ancora_cutile_b200 import kernels as K_
+        g_acc = anc.DBuf.zeros((a_owned,), np.float32, ctx)
+        g_src = anc.DBuf.zeros((a_owned,), np.uint16, ctx)
+        g_out = anc.DBuf.zeros((a_owned,), np.uint16, ctx)
+        reps = 10
+        for i in range(3 + reps):
+            if i == 3:
+                e0.record(ctx.stream)
+            K_.grad_accumulate(g_acc, g_src, g_out, a_owned, src_dtype="bf16", rounding="sr", seed=SEED_SR + 1,
+                               step=i, elem_offset=eng.a_begin, stream=ctx.stream, ctx=ctx)
+        e1.record(ctx.stream)
+        ctx.sync()
+        gp_ms = e0.elapsed_ms(e1) / reps
+        gp_gbs = 12.0 * a_owned / (gp_ms * 1e-3) / 1e9
+        out["grad_producer"] = {"bound": "hbm", "kernel": "grad_accumulate_kernel", "achieved": gp_gbs,
+                                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gp_gbs / peaks["hbm_gbs"],
+                                "bytes_per_elem": 12, "elems": a_owned, "ms": gp_ms,
+                                "note": "timed alone, arena larger than L2, not part of ms_per_step"}
+        for b in (g_acc, g_src, g_out):
+            b.free()
+
     # ---- end-to-end: host gradients in, bf16 weights out, through the public call path ----
     if not args.no_e2e:
         h2d = d2h = 0
