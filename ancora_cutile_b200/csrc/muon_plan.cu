@@ -375,8 +375,9 @@ int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t
     ANC_CUDA(cudaStreamSynchronize(ctx->stream));
     if (ctx->d_work) cudaFree(ctx->d_work);
     ctx->d_work = nullptr;
+    ctx->work_bytes = 0;
+    ANC_CUDA(cudaMalloc(&ctx->d_work, need * 2));
     ctx->work_bytes = need * 2;
-    ANC_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
   }
   int rc = anc_launch_fro_partial(ctx, X, (float *)ctx->d_work, E, M, N, st);
   if (rc) return rc;

@@ -43,35 +43,35 @@ int anc_ctx_create(int device, void *stream, anc_ctx **out) {
   anc_ctx *c = new anc_ctx();
   memset(c, 0, sizeof(*c));
   c->device = device;
+  auto fail = [c](int rc) {          // release whatever was set up so far
+    if (c->d_work) cudaFree(c->d_work);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c;
+    return rc;
+  };
   if (stream) {
     c->stream = (cudaStream_t)stream;
     c->own_stream = false;
   } else {
     cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
-    if (e != cudaSuccess) {
-      delete c;
-      return anc_cuda_fail(e, "cudaStreamCreate");
-    }
+    if (e != cudaSuccess) return fail(anc_cuda_fail(e, "cudaStreamCreate"));
     c->own_stream = true;
   }
-  cudaDeviceProp prop;
-  ANC_CUDA(cudaGetDeviceProperties(&prop, device));
-  c->sm_count = prop.multiProcessorCount;
-  if (prop.major != 10) {
-    anc_set_error("device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major,
-                  prop.minor);
-    if (c->own_stream) cudaStreamDestroy(c->stream);
-    delete c;
-    return ANC_E_UNSUPPORTED;
+  int major = 0, minor = 0;
+  cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) return fail(anc_cuda_fail(e, "cudaDeviceGetAttribute"));
+  if (major != 10) {
+    anc_set_error("device %d is sm_%d%d; this library holds sm_100a code only", device, major, minor);
+    return fail(ANC_E_UNSUPPORTED);
   }
   c->work_bytes = 1 << 20;
-  cudaError_t e = cudaMalloc(&c->d_work, c->work_bytes);
+  e = cudaMalloc(&c->d_work, c->work_bytes);
   if (e == cudaSuccess) e = cudaMalloc((void **)&c->d_status, 256);
   if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 256);
-  if (e != cudaSuccess) {
-    delete c;
-    return anc_cuda_fail(e, "ctx workspace");
-  }
+  if (e != cudaSuccess) return fail(anc_cuda_fail(e, "ctx workspace"));
   *out = c;
   return ANC_OK;
 }

@@ -3,6 +3,7 @@
 // is single-GPU and has no counterpart.  Collectives are issued on the caller's
 // stream; payloads are sent as bytes so no NCCL datatype enum is relied on.
 #include <dlfcn.h>
+#include <mutex>
 #include <nccl.h>
 #include <string.h>
 #include "anc_internal.h"
@@ -23,6 +24,7 @@ struct NcclApi {
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 NcclApi g_nccl;
+std::mutex g_nccl_mu;   // guards the one-time load
 
 int nccl_fail(ncclResult_t r, const char *what) {
   anc_set_error("NCCL error %d (%s) in %s", (int)r,
@@ -54,6 +56,7 @@ struct anc_comm {
 extern "C" {
 
 int anc_nccl_load(const char *path) {
+  std::lock_guard<std::mutex> lk(g_nccl_mu);
   if (g_nccl.handle) return ANC_OK;
   const char *cands[4] = {path, getenv("ANC_NCCL_PATH"), "libnccl.so.2", "libnccl.so"};
   for (const char *c : cands) {

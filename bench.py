@@ -166,7 +166,7 @@ def main():
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "moe"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--dump-digests", default=None, help="write a per-tensor fingerprint map to this file (rank 0)")
+    ap.add_argument("--dump-digests", default=None, help="write per-tensor fingerprints of the bf16 parameters and of the owned float32 masters to this file (rank r > 0: FILE.rankR)")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: fewer layers")
     ap.add_argument("--vocab", type=int, default=None, help="profiling only: smaller vocabulary")
     args = ap.parse_args()
@@ -401,11 +401,18 @@ def main():
     for name in shp:
         hsh.update(np.ascontiguousarray(bits[name]).tobytes())
     digest = hsh.hexdigest()
-    if args.dump_digests and rank == 0:
+    if args.dump_digests:
+        # every rank writes its own view: the bf16 parameters it holds after the exchange and the
+        # float32 masters of what it owns (which no exchange ever touches), so a mismatch can be
+        # placed either in the owner's arithmetic or in the transport
         per = {name: hashlib.blake2b(np.ascontiguousarray(bits[name]).tobytes(), digest_size=8).hexdigest()
                for name in shp}
-        with open(args.dump_digests, "w") as f:
-            json.dump({"world": world, "owner": {n: eng.m_owner.get(n, -1) for n in shp}, "digests": per}, f)
+        masters = {name: [int(lo), int(hi), hashlib.blake2b(np.ascontiguousarray(v).tobytes(), digest_size=8).hexdigest()]
+                   for name, (lo, hi, v) in eng.master().items()}
+        path = args.dump_digests if rank == 0 else f"{args.dump_digests}.rank{rank}"
+        with open(path, "w") as f:
+            json.dump({"world": world, "rank": rank, "owner": {n: eng.m_owner.get(n, -1) for n in shp},
+                       "digests": per, "masters": masters}, f)
     if dist is not None:
         box = [None] * world
         dist.all_gather_object(box, digest)
