@@ -19,6 +19,7 @@ first) -- so that a unit's exchange (and, in ``step_host``, its host copies) ove
 next unit's compute.
 """
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -150,7 +151,10 @@ class ResidentHybrid:
             for gi in range(self.muon.num_groups()):
                 _, cap, M, Nn = self.muon.group_info(gi)
                 self._pgroup[(M, Nn)] = (gi, cap)
-        self.host_chunk_elems = 64 << 20       # step_host cuts units to <= 128 MiB of bf16
+        # step_host cuts units to at most this many elements: its run time is the transfer time of
+        # all bytes plus the (transfer + compute) time of the LARGEST unit, so smaller units shorten
+        # the pipeline's tail until the Newton-Schulz batches get too small to fill the GPU
+        self.host_chunk_elems = int(os.environ.get("ANCORA_HOST_CHUNK_ELEMS", 32 << 20))
         self._sub_plans = []
         self.units = self._make_units(None)
         self._host_units = None
