@@ -325,6 +325,51 @@ class ResidentHybrid:
         for g in self.groups:
             self.comm.reduce_scatter_grads(self.m_g.ptr + g["base"] * it, g["per"], self.grad_dtype, si)
 
+    # ---------------------------------------------------------------- gradient accumulation
+    def enable_grad_accumulation(self):
+        """Allocates float32 accumulators with the layout of the two gradient arenas (4 B/param).
+        Micro-batch gradients keep arriving in the gradient arenas as before (``upload_grads``,
+        ``grad_view``); ``accumulate_grads`` folds them into the accumulators and
+        ``finalize_grads`` turns the sum into the bf16 gradients the step reads."""
+        assert self.grad_dtype == "bf16", "with float32 gradients accumulate in the gradient arenas themselves"
+        if getattr(self, "acc_a", None) is None:
+            self.acc_a = DBuf.zeros((self.a_padded,), np.float32, self.ctx)
+            self.acc_m = DBuf.zeros((self.m_total,), np.float32, self.ctx)
+            self.acc_count = 0
+
+    def accumulate_grads(self, si=None):
+        """acc += the gradients now in the gradient arenas (one sweep per arena, all regions: a
+        data-parallel replica holds local gradients for every parameter)."""
+        from . import kernels
+        for acc, g, n in ((self.acc_a, self.a_g, self.a_padded), (self.acc_m, self.m_g, self.m_total)):
+            kernels.grad_accumulate(acc, g, None, n, src_dtype="bf16", stream=si, ctx=self.ctx)
+        self.acc_count += 1
+
+    def finalize_grads(self, si=None, scale=None, rounding="sr", seed=None, reduce=True):
+        """Last micro-batch: acc += the gradients in the arenas, then (world > 1 and ``reduce``) the
+        float32 accumulators are reduce-scattered to their ZeRO-1 owners, and one sweep per arena
+        writes bf16(acc * scale) back into the gradient arenas and clears the accumulators.
+        ``scale`` defaults to 1 / (micro-batches * world).  Stochastic rounding draws from the
+        producer's own Philox stream (seed + 1 of the step's by default, counter = position in the
+        arena and the number of the step about to run), so it is reproducible for a fixed world size."""
+        from . import kernels
+        self.accumulate_grads(si)
+        multi = reduce and self.world > 1
+        if multi:
+            assert self.comm is not None, "finalize_grads needs an NCCL communicator to reduce"
+            self.comm.reduce_scatter_grads(self.acc_a.ptr, self.a_per, "f32", si)
+            for g in self.groups:
+                self.comm.reduce_scatter_grads(self.acc_m.ptr + g["base"] * 4, g["per"], "f32", si)
+        if scale is None:
+            scale = 1.0 / (self.acc_count * (self.world if multi else 1))
+        seed = (self.seed + 1) if seed is None else seed
+        # the Muon arena's stream starts after the AdamW arena's, so no two elements share a counter
+        for acc, g, n, off in ((self.acc_a, self.a_g, self.a_padded, 0),
+                               (self.acc_m, self.m_g, self.m_total, self.a_padded)):
+            kernels.grad_accumulate(acc, None, g, n, elem_offset=off, scale=scale, rounding=rounding, seed=seed,
+                                    step=self.t + 1, zero_after=True, stream=si, ctx=self.ctx)
+        self.acc_count = 0
+
     # ---------------------------------------------------------------- graph replay
     def capture_step(self, si=None, horizon=4096):
         """Captures one whole step into a CUDA graph whose replay advances the optimizer by one
@@ -577,8 +622,10 @@ class ResidentHybrid:
             self.muon.free()
             self.muon = None
         for b in (self.a_p16, self.a_g, self.a_p32, self.a_m, self.a_v, self.m_p16, self.m_g,
-                  self.m_p32, self.m_buf):
-            b.free()
+                  self.m_p32, self.m_buf, getattr(self, "acc_a", None), getattr(self, "acc_m", None)):
+            if b is not None:
+                b.free()
+        self.acc_a = self.acc_m = None
         for grp in (self._pin_g[:2] if self._pin_g else ()), (self._pin_w or ()):
             for p in grp:
                 p.free()

@@ -107,3 +107,49 @@ def test_sr_downcast_is_unbiased(ctx):
     # standard error of the mean of a two-point distribution of width <= 1 ulp(bf16)
     assert np.all(np.abs(tot / steps - acc) <= 6 * ulp / np.sqrt(steps) + 1e-12)
     d_acc.free(); d_g.free()
+
+
+def test_engine_accumulates_micro_batches_and_steps_on_the_sum(ctx):
+    """Three micro-batches folded into the float32 accumulators, one sweep that writes the bf16
+    gradients of the step: bits equal the oracle's, and the step equals a step on those bits."""
+    from ancora_cutile_b200 import shapes as S
+    shp = S.qwen3_0_6b_shapes(n_layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=2048)
+    params = S.synthetic_params(shp, seed=5)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    kw = dict(adamw_kw=dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, wd=0.1), grad_dtype="bf16", rounding="sr",
+              seed=7, schedule=anc.PE_SCHEDULE, ctx=ctx)
+    micro = [S.synthetic_grads_bf16(shp, seed=60 + k) for k in range(3)]
+    eng = anc.ResidentHybrid(params, mu, nd, **kw)
+    eng.enable_grad_accumulation()
+    for k, g in enumerate(micro):
+        eng.upload_grads(g, ctx.stream)
+        if k < 2:
+            eng.accumulate_grads(ctx.stream)
+        else:
+            eng.finalize_grads(ctx.stream)             # scale 1/3, SR, seed 8, step 1
+    ctx.sync()
+    summed = {}
+    for n in shp:
+        acc = np.zeros(int(np.prod(shp[n])), np.float32)
+        for g in micro:
+            acc, _ = grad_ref.grad_accumulate(acc, g[n].reshape(-1), want_g16=False)
+        off = eng.a_off[n] if n in eng.a_off else eng.a_padded + eng.m_off[n]
+        _, bits = grad_ref.grad_accumulate(acc, None, scale=1.0 / 3.0, rounding="sr", seed=8, step=1, elem_offset=off)
+        summed[n] = bits.reshape(shp[n])
+        assert np.array_equal(eng.grad_view(n).to_numpy(), summed[n]), n
+    assert not eng.acc_a.to_numpy().any() and not eng.acc_m.to_numpy().any()
+    eng.step(ctx.stream)
+    ctx.sync()
+    got, _ = eng.download_weights_bits()
+    got = {n: b.copy() for n, b in got.items()}
+    eng.free()
+    ref = anc.ResidentHybrid(params, mu, nd, **kw)
+    ref.upload_grads(summed, ctx.stream)
+    ref.step(ctx.stream)
+    ctx.sync()
+    want, _ = ref.download_weights_bits()
+    for n in shp:
+        assert np.array_equal(got[n], want[n]), n
+    ref.free()
+    assert ctx.status() == 0
