@@ -37,6 +37,14 @@ __device__ __forceinline__ uint32_t rne16(float x) {
 }
 __device__ __forceinline__ float bf16_f32(uint32_t h) { return __uint_as_float(h << 16); }
 
+// Column swizzle of the 64x64 transposition tile: element (row, col) lives in 8-element column
+// group (col / 8) ^ ((row / 8) % 8).  Rows stay 16-byte vectors for the row-wise side, and the
+// 16-bit column-wise side finds rows 8 or 16 apart in different banks (the 144-byte pitch alone
+// maps them to the same bank: 4- and 8-way conflicts).
+__device__ __forceinline__ int swz_col(int row, int col) {
+  return ((((col >> 3) ^ (row >> 3)) & 7) << 3) | (col & 7);
+}
+
 // One 64x64 tile of one weight.  Thread t: columns 8*(t%8)..+7, rows t/8 and t/8 + 32,
 // 128-bit accesses.  Returns this thread's sum of squares of the bf16-rounded u values
 // (added in element order: first row left to right, then the second row).
@@ -88,7 +96,7 @@ __device__ __forceinline__ float momentum_tile(const MomW &w, int slot, uint16_t
     const uint4 pk = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16),
                                 h[6] | (h[7] << 16));
     if (!w.tr) *reinterpret_cast<uint4 *>(wx + idx) = pk;
-    else *reinterpret_cast<uint4 *>(&sm[rl][c8]) = pk;
+    else *reinterpret_cast<uint4 *>(&sm[rl][swz_col(rl, c8)]) = pk;
   }
   if (w.tr) {
     __syncthreads();
@@ -97,8 +105,11 @@ __device__ __forceinline__ float momentum_tile(const MomW &w, int slot, uint16_t
     const int rr = (threadIdx.x & 3) * 16;
     uint32_t pk[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      pk[j] = (uint32_t)sm[rr + 2 * j][oc] | ((uint32_t)sm[rr + 2 * j + 1][oc] << 16);
+    for (int j = 0; j < 8; ++j) {
+      const int ra = rr + 2 * j;               // ra and ra + 1 share one swizzle
+      const int sc = swz_col(ra, oc);
+      pk[j] = (uint32_t)sm[ra][sc] | ((uint32_t)sm[ra + 1][sc] << 16);
+    }
     uint16_t *dst = wx + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
     reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
@@ -121,8 +132,8 @@ __device__ __forceinline__ void update_tile(const UpdW &w, int slot, const uint1
     const uint16_t *src = wo + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
     const uint4 a = reinterpret_cast<const uint4 *>(src)[0];
     const uint4 b = reinterpret_cast<const uint4 *>(src)[1];
-    reinterpret_cast<uint4 *>(&sm[oc][rr])[0] = a;
-    reinterpret_cast<uint4 *>(&sm[oc][rr])[1] = b;
+    *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr)]) = a;
+    *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr + 8)]) = b;
     __syncthreads();
   }
 #pragma unroll
@@ -142,7 +153,7 @@ __device__ __forceinline__ void update_tile(const UpdW &w, int slot, const uint1
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][rl]);
+      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][swz_col(c8 + j, rl)]);
     }
     const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
     float pn[8];
