@@ -297,8 +297,8 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
     const int oc = threadIdx.x >> 2;
     const int rr = (threadIdx.x & 3) * 16;
     const uint16_t *src = wo + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
-    reinterpret_cast<uint4 *>(&sm[oc][rr])[0] = reinterpret_cast<const uint4 *>(src)[0];
-    reinterpret_cast<uint4 *>(&sm[oc][rr])[1] = reinterpret_cast<const uint4 *>(src)[1];
+    *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr)]) = reinterpret_cast<const uint4 *>(src)[0];
+    *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr + 8)]) = reinterpret_cast<const uint4 *>(src)[1];
     __syncthreads();
   }
   uint32_t h[2][8];
@@ -319,7 +319,7 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][rl]);
+      for (int j = 0; j < 8; ++j) o[j] = bf16_f32(sm[c8 + j][swz_col(c8 + j, rl)]);
     }
     const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
     float pn[8];
@@ -337,7 +337,7 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
   if (x.p16_t) {
 #pragma unroll
     for (int k = 0; k < 2; ++k)
-      *reinterpret_cast<uint4 *>(&sm[r0 + 32 * k][c8]) =
+      *reinterpret_cast<uint4 *>(&sm[r0 + 32 * k][swz_col(r0 + 32 * k, c8)]) =
           make_uint4(h[k][0] | (h[k][1] << 16), h[k][2] | (h[k][3] << 16), h[k][4] | (h[k][5] << 16),
                      h[k][6] | (h[k][7] << 16));
   }
@@ -371,8 +371,11 @@ __device__ __forceinline__ void update_tile_extras(const UpdW &w, const UpdX &x,
     const int rr = (threadIdx.x & 3) * 16;
     uint32_t pk[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      pk[j] = (uint32_t)sm[rr + 2 * j][oc] | ((uint32_t)sm[rr + 2 * j + 1][oc] << 16);
+    for (int j = 0; j < 8; ++j) {
+      const int ra = rr + 2 * j;
+      const int sc = swz_col(ra, oc);
+      pk[j] = (uint32_t)sm[ra][sc] | ((uint32_t)sm[ra + 1][sc] << 16);
+    }
     uint16_t *dst = x.p16_t + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
     reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
