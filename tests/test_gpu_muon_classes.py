@@ -121,3 +121,58 @@ def test_misaligned_shape_raises(ctx):
         anc.Muon({"router": np.zeros((1024, 16), np.float32)}, ctx=ctx)
     with pytest.raises(AssertionError):
         anc.Muon({"gain": np.zeros((128,), np.float32)}, ctx=ctx)
+
+
+@pytest.mark.parametrize("shape", [(512, 512), (1024, 512)])
+def test_descends_on_a_quadratic_like_the_host_optimizer(ctx, shape):
+    """Minimise 0.5 * ||W - T||^2 with g = W - T for 30 steps from W = 0: the loss must fall below
+    0.2 of its start and stay within 3x the host optimizer's ratio + 0.05
+    (tests/kernels/_probe_device_muon.py:72-100, square and tall)."""
+    K, N = shape
+    rng = np.random.default_rng(1)
+    T = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    host = muon_ref.HostMuon({"w": np.zeros(shape, np.float32)}, schedule=None)
+    dev = anc.Muon({"w": np.zeros(shape, np.float32)}, lr=0.02, momentum=0.95, ns_steps=5, schedule=None, ctx=ctx)
+    lh, ld = [], []
+    for _ in range(30):
+        g = host.w["w"] - T
+        lh.append(0.5 * float(np.sum(g * g)))
+        host.step({"w": g})
+        g = dev.master()["w"] - T
+        ld.append(0.5 * float(np.sum(g * g)))
+        dev.step({"w": g}, None)
+    dev.free()
+    drop_d, drop_h = ld[-1] / ld[0], lh[-1] / lh[0]
+    assert drop_d < 0.2 and drop_d < 3 * drop_h + 0.05, (drop_d, drop_h)
+
+
+def test_interleaved_weights_of_three_shapes_do_not_contaminate_each_other(ctx):
+    """Square, wide and tall ResidentMuon objects built over one MuonScratch and stepped in turn
+    within every step, each against its own host optimizer (tests/kernels/_probe_device_muon.py:104-138:
+    shared scratch, transposed path, cos > 0.99, rel < 0.06 after 5 steps)."""
+    shapes = [(256, 256), (256, 512), (512, 256)]
+    rng = np.random.default_rng(0)
+    sc = anc.MuonScratch(shapes)
+    items = []
+    for K, N in shapes:
+        W0 = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+        p32, p16 = anc.DBuf(W0, ctx), anc.DBuf(f32_to_bf16_bits(W0), ctx)
+        g_dev = anc.DBuf.zeros((K, N), np.float32, ctx)
+        items.append((W0, muon_ref.HostMuon({"w": W0.copy()}, schedule=None), p32, p16,
+                      anc.ResidentMuon(p32, p16, K, N, sc, schedule=None, ctx=ctx), g_dev))
+    for _ in range(5):
+        for W0, host, p32, p16, rm, g_dev in items:
+            g = rng.standard_normal(W0.shape).astype(np.float32)
+            host.step({"w": g})
+            g_dev.upload(g)
+            rm.step(g_dev, ctx.stream, 0.02)
+    ctx.sync()
+    assert ctx.status() == 0
+    for W0, host, p32, p16, rm, g_dev in items:
+        c, r = cos_rel(W0 - p32.to_numpy(), W0 - host.w["w"])
+        assert c > 0.99 and r < 0.06, (W0.shape, c, r)
+        assert np.array_equal(p16.to_numpy(), f32_to_bf16_bits(p32.to_numpy()))
+        rm.free()
+        for b in (p32, p16, g_dev):
+            b.free()
+    sc.free()

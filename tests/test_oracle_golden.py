@@ -144,3 +144,23 @@ def test_oracle_quant_decodes_within_e4m3_step():
     blockmax = np.abs(x).reshape(4, 32, 96).max(axis=1).repeat(32, axis=0)
     assert np.all(np.abs(back - x) <= blockmax * 2.0 ** -4 + 1e-30)       # 3 mantissa bits, block-relative
     assert np.all(q[np.abs(x) == blockmax] != 0)
+
+
+def test_polar_express_orthogonalises_better_than_keller_in_five_steps():
+    """Host-only property the reference checks in tests/kernels/_probe_polar_express.py: on
+    matrices with spread singular values, 5 Polar-Express iterations leave a smaller
+    orthogonality error than 5 Keller iterations, and a sixth PE step (last triple repeated,
+    muon_ns.py:38-42) does not make it worse."""
+    from oracle import muon_ref
+    rng = np.random.default_rng(0)
+    for M, N in ((128, 128), (128, 384)):
+        W = (rng.standard_normal((M, N)) @ np.diag(rng.uniform(0.1, 3.0, N))).astype(np.float32)
+
+        def err(Y):
+            return float(np.linalg.norm(Y @ Y.T - np.eye(M, dtype=Y.dtype)) / np.sqrt(M))
+
+        k5 = err(muon_ref.ns_fp32(W, 5, None))
+        p5 = err(muon_ref.ns_fp32(W, 5, muon_ref.PE_SCHEDULE))
+        p6 = err(muon_ref.ns_fp32(W, 6, muon_ref.PE_SCHEDULE))
+        assert p5 < k5, (M, N, p5, k5)
+        assert p6 <= p5 * 1.05, (M, N, p6, p5)
