@@ -1,0 +1,119 @@
+"""Where every parameter lives in the two arenas of a rank, and the units a step walks.
+
+Pure host arithmetic (no device, no library): given the parameter shapes, the Muon routing and
+(rank, world) it fixes
+
+  AdamW arena : every tensor at a 64-element-aligned global offset, the arena padded to
+                world * per_rank; rank r owns the contiguous slice [r * per, (r + 1) * per).
+  Muon arena  : [shape group][owner rank][matrix]; inside a group every rank's region has the
+                same padded size ``per``, so a group is exchanged in place; the float32 state of
+                the owned matrices is packed [shape group][matrix] (``m_own_off``).
+
+and cuts a step into units, each a contiguous span of this rank's share of one arena.  The
+reference keeps per-name buffers on one GPU (ancora/optim/adamw.py:76-87, optim/muon.py:236-254);
+arenas exist here so that one launch covers all tensors and one exchange covers a unit.
+"""
+import numpy as np
+
+from .zero1 import partition_by_group, slice_bounds
+
+
+def _numel(shape):
+    return int(np.prod(shape, dtype=np.int64))
+
+
+def _align_up(x, a):
+    return -(-x // a) * a
+
+
+class ArenaLayout:
+    def __init__(self, shapes, muon_names, rank=0, world=1):
+        """shapes: {name: shape} in registration order (identical on every rank)."""
+        self.rank, self.world = int(rank), int(world)
+        assert 0 <= self.rank < self.world
+        mset = set(muon_names)
+        self.shapes = {n: tuple(int(x) for x in s) for n, s in shapes.items()}
+        self.muon_names = [n for n in self.shapes if n in mset]
+        self.adamw_names = [n for n in self.shapes if n not in mset]
+        W, R = self.world, self.rank
+
+        # AdamW arena
+        self.a_off, off = {}, 0
+        for n in self.adamw_names:
+            self.a_off[n] = off
+            off = _align_up(off + _numel(self.shapes[n]), 64)
+        self.a_total = off
+        self.a_per, self.a_padded = slice_bounds(max(off, 64), W, 64)
+        self.a_begin, self.a_end = R * self.a_per, (R + 1) * self.a_per
+
+        # Muon arenas
+        mshapes = [self.shapes[n] for n in self.muon_names]
+        self.owner, self.load = partition_by_group(mshapes, W)
+        self.m_owner = dict(zip(self.muon_names, self.owner))
+        self.groups = []                   # dicts: key, elems, per, base, names (by rank), own_base, total
+        self.m_off, self.m_own_off = {}, {}
+        base = own = 0
+        for key in sorted({(min(s), max(s)) for s in mshapes}):
+            e = key[0] * key[1]
+            by_rank = [[] for _ in range(W)]
+            for n, r in zip(self.muon_names, self.owner):
+                if (min(self.shapes[n]), max(self.shapes[n])) == key:
+                    by_rank[r].append(n)
+            per = max(len(x) for x in by_rank) * e
+            g = dict(key=key, elems=e, per=per, base=base, names=by_rank, own_base=own,
+                     total=sum(len(x) for x in by_rank) * e)
+            for r in range(W):
+                for k, n in enumerate(by_rank[r]):
+                    self.m_off[n] = base + r * per + k * e
+            for k, n in enumerate(by_rank[R]):
+                self.m_own_off[n] = own + k * e
+            base += W * per
+            own += len(by_rank[R]) * e
+            self.groups.append(g)
+        self.m_total = max(base, 64)
+        self.m_owned_elems = own
+        self.gmap = {g["key"]: g for g in self.groups}
+
+    def owned_range(self, name):
+        """(start, stop) flat element range of ``name`` whose state this rank holds."""
+        n = _numel(self.shapes[name])
+        if name in self.a_off:
+            o = self.a_off[name]
+            lo, hi = max(o, self.a_begin), min(o + n, self.a_end)
+            return (lo - o, hi - o) if lo < hi else (0, 0)
+        return (0, n) if self.m_owner[name] == self.rank else (0, 0)
+
+    def make_units(self, batch_cap=None, max_elems=None, halve_from=None):
+        """Units in execution order: ("adamw", begin, end) over arena-0 elements, then
+        ("muon", group key, first, count) over this rank's matrices of each shape group, groups
+        by descending size (the last unit's exchange or copy-out is the one nothing overlaps,
+        so the smallest goes last).  ``batch_cap[key]`` bounds a Muon unit by the scratch batch
+        of the plan; ``max_elems`` cuts units into sub-ranges of at most that many elements (host
+        pipelining); ``halve_from`` cuts a group with at least that many matrices of this rank in
+        two, so that the first half's exchange starts while the second half computes."""
+        units = []
+        if max_elems is None:
+            units.append(("adamw", self.a_begin, self.a_end))
+        else:
+            step = max(64, max_elems // 64 * 64)
+            for lo in range(self.a_begin, self.a_end, step):
+                units.append(("adamw", lo, min(lo + step, self.a_end)))
+        for g in sorted(self.groups, key=lambda g: -g["total"]):
+            mine = len(g["names"][self.rank])
+            if not mine:
+                continue
+            cap = mine if batch_cap is None else batch_cap[g["key"]]
+            per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
+            if halve_from is not None and mine >= halve_from:
+                per = min(per, -(-mine // 2))
+            for first in range(0, mine, per):
+                units.append(("muon", g["key"], first, min(per, mine - first)))
+        return units
+
+    def unit_span(self, unit):
+        """(arena index, element offset, element count) of a unit's span in the bf16 parameter
+        and gradient arenas (arena 0 = AdamW, 1 = Muon)."""
+        if unit[0] == "adamw":
+            return 0, unit[1], unit[2] - unit[1]
+        g = self.gmap[unit[1]]
+        return 1, g["base"] + self.rank * g["per"] + unit[2] * g["elems"], unit[3] * g["elems"]

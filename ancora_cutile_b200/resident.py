@@ -24,11 +24,11 @@ import os
 import numpy as np
 
 from . import _lib as L
-from .adamw import ResidentAdamW, align_up
+from .adamw import ResidentAdamW
 from .bf16 import bits_to_f32, f32_to_bf16_bits
 from .buffers import DBuf, Event, PinnedArray, get_context
 from .muon import MuonPlan, _UNSET, _schedule
-from .zero1 import ns_cost, partition_by_group, slice_bounds
+from .layout import ArenaLayout
 
 
 def _numel(shape):
@@ -56,22 +56,16 @@ class ResidentHybrid:
         self.nccl_overlap = comm is not None
         gdt = np.uint16 if grad_dtype == "bf16" else np.float32
         self._gdt = np.dtype(gdt)
-        mset = set(muon_names)
-        self.muon_names = [n for n in params if n in mset]
-        self.adamw_names = [n for n in params if n not in mset]
-        self.shapes = {n: tuple(p.shape) for n, p in params.items()}
+        lay = ArenaLayout({n: p.shape for n, p in params.items()}, muon_names, rank, world)
+        self.layout = lay
+        self.muon_names, self.adamw_names, self.shapes = lay.muon_names, lay.adamw_names, lay.shapes
         nd = set(no_decay_names)
         c = self.ctx
         W, R = self.world, self.rank
 
         # ---------------- AdamW arena
-        self.a_off, off = {}, 0
-        for n in self.adamw_names:
-            self.a_off[n] = off
-            off = align_up(off + _numel(self.shapes[n]), 64)
-        self.a_total = off
-        self.a_per, self.a_padded = slice_bounds(max(off, 64), W, 64)
-        self.a_begin, self.a_end = R * self.a_per, (R + 1) * self.a_per
+        self.a_off, self.a_total = lay.a_off, lay.a_total
+        self.a_per, self.a_padded, self.a_begin, self.a_end = lay.a_per, lay.a_padded, lay.a_begin, lay.a_end
         self.a_p16 = DBuf.zeros((self.a_padded,), np.uint16, c)
         self.a_g = DBuf.zeros((self.a_padded,), gdt, c)
         self.a_p32 = DBuf.zeros((self.a_per,), np.float32, c)
@@ -98,31 +92,9 @@ class ResidentHybrid:
             self.adamw.set_range(self.a_begin, self.a_end)
 
         # ---------------- Muon arenas: [group][owner][matrix]
-        mshapes = [self.shapes[n] for n in self.muon_names]
-        self.owner, self.load = partition_by_group(mshapes, W)
-        self.m_owner = dict(zip(self.muon_names, self.owner))
-        gkeys = sorted({(min(s), max(s)) for s in mshapes})
-        self.groups = []                       # dicts: key, elems, per, base, names_by_rank, own_base
-        base = own = 0
-        self.m_off, self.m_own_off = {}, {}    # global arena offset / offset in the owned fp32 arenas
-        for key in gkeys:
-            e = key[0] * key[1]
-            by_rank = [[] for _ in range(W)]
-            for n, r in zip(self.muon_names, self.owner):
-                if (min(self.shapes[n]), max(self.shapes[n])) == key:
-                    by_rank[r].append(n)
-            per = max(len(x) for x in by_rank) * e
-            g = dict(key=key, elems=e, per=per, base=base, names=by_rank, own_base=own,
-                     total=sum(len(x) for x in by_rank) * e)
-            for r in range(W):
-                for k, n in enumerate(by_rank[r]):
-                    self.m_off[n] = base + r * per + k * e
-            for k, n in enumerate(by_rank[R]):
-                self.m_own_off[n] = own + k * e
-            base += W * per
-            own += len(by_rank[R]) * e
-            self.groups.append(g)
-        self.m_total = max(base, 64)
+        self.owner, self.load, self.m_owner = lay.owner, lay.load, lay.m_owner
+        self.groups, self.m_off, self.m_own_off = lay.groups, lay.m_off, lay.m_own_off
+        self.m_total, own = lay.m_total, lay.m_owned_elems
         self.m_p16 = DBuf.zeros((self.m_total,), np.uint16, c)
         self.m_g = DBuf.zeros((self.m_total,), gdt, c)
         self.m_p32 = DBuf.zeros((max(own, 64),), np.float32, c)
@@ -145,7 +117,7 @@ class ResidentHybrid:
         # Units of work, each a contiguous span of this rank's share of an arena:
         #   ("adamw", plan, begin, end)            arena-0 elements [begin, end)
         #   ("muon", plan group, first, count)     matrices [first, first+count) of a shape group
-        self._gmap = {g["key"]: g for g in self.groups}
+        self._gmap = lay.gmap
         self._pgroup = {}                      # shape key -> (plan group index, scratch batch)
         if self.muon is not None:
             for gi in range(self.muon.num_groups()):
@@ -206,28 +178,18 @@ class ResidentHybrid:
         cuts a group with at least that many matrices of this rank in two, so that the first
         half's exchange starts while the second half computes."""
         units = []
-        R = self.rank
-        if max_elems is None:
-            units.append(("adamw", self.adamw, self.a_begin, self.a_end))
-        else:
-            step = max(64, max_elems // 64 * 64)
-            for lo in range(self.a_begin, self.a_end, step):
-                hi = min(lo + step, self.a_end)
+        caps = {key: cap for key, (_, cap) in self._pgroup.items()}
+        for u in self.layout.make_units(caps, max_elems, halve_from):
+            if u[0] == "muon":
+                units.append(("muon", self._pgroup[u[1]][0], u[2], u[3], u[1]))
+            elif max_elems is None:
+                units.append(("adamw", self.adamw, u[1], u[2]))
+            else:                              # a sub-range of the slice gets a plan of its own
                 pl = ResidentAdamW(self._adamw_tensors, grad_dtype=self.grad_dtype, rounding=self.rounding,
                                    seed=self.seed, ctx=self.ctx)
-                pl.set_range(lo, hi)
+                pl.set_range(u[1], u[2])
                 self._sub_plans.append(pl)
-                units.append(("adamw", pl, lo, hi))
-        for g in sorted(self.groups, key=lambda g: -g["total"]):
-            mine = len(g["names"][R])
-            if not mine:
-                continue
-            gi, cap = self._pgroup[g["key"]]
-            per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
-            if halve_from is not None and mine >= halve_from:
-                per = min(per, -(-mine // 2))
-            for first in range(0, mine, per):
-                units.append(("muon", gi, first, min(per, mine - first), g["key"]))
+                units.append(("adamw", pl, u[1], u[2]))
         return units
 
     def unit_span(self, unit):

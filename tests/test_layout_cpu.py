@@ -1,0 +1,143 @@
+"""CPU: the arena layout and the unit lists of the ZeRO-1 engine (pure host arithmetic), for
+1/2/4/8 ranks on the Qwen3-0.6B and MoE-family shapes, plus two gloo ranks that exchange their
+spans and check that together they cover every parameter exactly once."""
+import os
+
+import numpy as np
+import pytest
+
+from ancora_cutile_b200 import shapes as S
+from ancora_cutile_b200.hybrid import default_is_muon
+from ancora_cutile_b200.layout import ArenaLayout
+
+
+def _family(which):
+    shp = S.qwen3_0_6b_shapes() if which == "qwen3" else S.moe_family_shapes()
+    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    return shp, mu
+
+
+def _numel(s):
+    return int(np.prod(s, dtype=np.int64))
+
+
+def _tiles(spans, lo, hi):
+    """True when the (offset, count) spans tile [lo, hi) exactly, in any order."""
+    pos = lo
+    for o, n in sorted(spans):
+        if o != pos or n <= 0:
+            return False
+        pos = o + n
+    return pos == hi
+
+
+@pytest.mark.parametrize("which", ["qwen3", "moe"])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_layout_is_the_same_on_every_rank_and_partitions_everything(which, world):
+    shp, mu = _family(which)
+    lays = [ArenaLayout(shp, mu, r, world) for r in range(world)]
+    a = lays[0]
+    for b in lays[1:]:
+        assert b.a_off == a.a_off and b.m_off == a.m_off and b.owner == a.owner
+        assert [(g["key"], g["base"], g["per"]) for g in b.groups] == [(g["key"], g["base"], g["per"]) for g in a.groups]
+    # AdamW: 64-aligned offsets in registration order, slices tile the padded arena
+    assert all(o % 64 == 0 for o in a.a_off.values())
+    assert _tiles([(l.a_begin, l.a_end - l.a_begin) for l in lays], 0, a.a_padded)
+    assert a.a_padded >= a.a_total and a.a_per % 64 == 0
+    # Muon: every matrix inside its owner's region of its group, no two matrices overlap
+    spans = []
+    for n in mu:
+        g = a.gmap[(min(shp[n]), max(shp[n]))]
+        r = a.m_owner[n]
+        lo = g["base"] + r * g["per"]
+        assert lo <= a.m_off[n] and a.m_off[n] + _numel(shp[n]) <= lo + g["per"], n
+        spans.append((a.m_off[n], _numel(shp[n])))
+    spans.sort()
+    assert all(spans[i][0] + spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
+    assert a.m_total >= spans[-1][0] + spans[-1][1]
+    # state ownership: over all ranks the owned ranges of a tensor partition it
+    for n in shp:
+        got = [l.owned_range(n) for l in lays]
+        assert _tiles([(s, e - s) for s, e in got if e > s], 0, _numel(shp[n])), n
+    assert sum(l.m_owned_elems for l in lays) == sum(_numel(shp[n]) for n in mu)
+
+
+@pytest.mark.parametrize("which", ["qwen3", "moe"])
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("mode", ["plain", "halved", "host_chunks", "capped"])
+def test_units_cover_exactly_what_the_rank_owns(which, world, mode):
+    shp, mu = _family(which)
+    for r in range(world):
+        lay = ArenaLayout(shp, mu, r, world)
+        caps = {g["key"]: max(1, min(8, len(g["names"][r]))) for g in lay.groups} if mode == "capped" else None
+        units = lay.make_units(caps, 16 << 20 if mode == "host_chunks" else None, 8 if mode == "halved" else None)
+        spans = {0: [], 1: []}
+        for u in units:
+            arena, off, n = lay.unit_span(u)
+            spans[arena].append((off, n))
+            if mode == "host_chunks":
+                assert n <= 16 << 20 or (u[0] == "muon" and u[3] == 1)
+            if caps and u[0] == "muon":
+                assert u[3] <= caps[u[1]]
+        assert _tiles(spans[0], lay.a_begin, lay.a_end)
+        own = sorted((lay.m_off[n], _numel(shp[n])) for n in mu if lay.m_owner[n] == r)
+        covered = sorted(spans[1])
+        # the unit spans of a group are contiguous runs over this rank's matrices of the group
+        assert sum(n for _, n in covered) == sum(n for _, n in own)
+        merged = []
+        for o, n in own:
+            if merged and merged[-1][0] + merged[-1][1] == o:
+                merged[-1] = (merged[-1][0], merged[-1][1] + n)
+            else:
+                merged.append((o, n))
+        for o, n in covered:
+            assert any(mo <= o and o + n <= mo + mn for mo, mn in merged), (o, n)
+        # AdamW first, then groups by descending size
+        kinds = [u[0] for u in units]
+        assert kinds == sorted(kinds, key=lambda k: k != "adamw")
+        sizes = [lay.gmap[u[1]]["total"] for u in units if u[0] == "muon"]
+        assert sizes == sorted(sizes, reverse=True)
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    shp, mu = _family("qwen3")
+    lay = ArenaLayout(shp, mu, rank, world)
+    mine = dict(rank=rank, spans=[lay.unit_span(u) for u in lay.make_units()], a_padded=lay.a_padded,
+                groups=[(g["key"], g["base"], g["per"], [len(x) for x in g["names"]]) for g in lay.groups])
+    box = [None] * world
+    dist.all_gather_object(box, mine)
+    if rank == 0:
+        q.put(box)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_exchange_complementary_spans():
+    """What each rank would send in the exchange: the two ranks' AdamW spans tile the padded arena,
+    and inside every shape group rank r's span starts at base + r * per (the in-place all-gather's
+    slot) and holds exactly its matrices."""
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [mpc.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    box = q.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert box[0]["groups"] == box[1]["groups"]
+    a_spans = [(o, n) for b in box for (arena, o, n) in b["spans"] if arena == 0]
+    assert _tiles(a_spans, 0, box[0]["a_padded"])
+    shp, _ = _family("qwen3")
+    for key, base, per, counts in box[0]["groups"]:
+        e = key[0] * key[1]
+        for b in box:
+            r = b["rank"]
+            mine = [(o, n) for (arena, o, n) in b["spans"] if arena == 1 and base <= o < base + 2 * per]
+            assert _tiles(mine, base + r * per, base + r * per + counts[r] * e), (key, r)
