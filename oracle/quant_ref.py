@@ -3,8 +3,13 @@
 Follows ancora/kernels/quant.py:56-68 (`_quant_mxfp8_w`): blocks of 32 along K (axis 0);
 per block and column the E8M0 scale byte is ``max(exponent_bits(max|w|) - 7, 0)`` (floor
 exponent), the scale ``2**(byte-127)`` and the stored value ``RNE_e4m3fn(w / scale)``.
-The reference kernel only runs on a GPU, so this restatement is pinned by the formula and by
-the decode check below, not by reference outputs: parity unpinned by reference outputs.
+The reference kernel only runs on a GPU, so the block formula (floor-exponent scale byte) is a
+restatement by reading: parity of the scale rule is unpinned by reference outputs.  What the
+reference's host helpers can pin is pinned by fixtures recorded from them
+(tests/golden/e4m3.npz: `_e4m3_table`, `f32_to_e4m3`, `dequantize_rowblock`, quant.py:92-175):
+the code table, the nearest-value rounding away from exact ties, the block dequantisation.  At
+exact ties the kernels' conversion is round-to-nearest-even (followed here); the host helper
+rounds ties to the smaller magnitude.
 """
 import numpy as np
 

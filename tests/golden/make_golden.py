@@ -14,6 +14,8 @@ before importing.  Only host (numpy) code of the reference is executed:
   ancora.optim.muon._bf                       -> bf16.npz
 * ancora.kernels.muon_ns.PE_SCHEDULE/_coef_at,
   ancora.optim.hybrid.default_is_muon         -> tables.json
+* ancora.kernels.quant._e4m3_table/f32_to_e4m3/
+  dequantize_rowblock (host helpers)          -> e4m3.npz
 
 The reference's AdamW runs only on a GPU (cuda.tile kernel); it has no host
 function to call, so AdamW has no file here: its oracle is pinned by the formula
@@ -104,6 +106,22 @@ def main(ref_root):
     }
     with open(os.path.join(HERE, "tables.json"), "w") as f:
         json.dump(tables, f, indent=1, sort_keys=True)
+
+    # 6. E4M3 / MXFP8 host helpers of ancora/kernels/quant.py (its own generator, so the files
+    #    above do not depend on this section): the 256-entry decode table, the host rounding
+    #    f32_to_e4m3 (nearest, ties to the smaller magnitude: it differs from the device
+    #    conversion's ties-to-even only at exact ties) and dequantize_rowblock
+    from ancora.kernels.quant import _e4m3_table, f32_to_e4m3, dequantize_rowblock
+    rq = np.random.default_rng(77)
+    w = (rq.standard_normal(8192) * np.exp(rq.uniform(-4, 6, 8192))).astype(np.float32)
+    w16 = _bits_f32(_bf16_bits(w))                               # bf16-valued inputs: many exact ties
+    xq = np.concatenate([w, w16, np.array([0.0, -0.0, 448.0, -448.0, 464.0, 1e9, 2.0 ** -9, 2.0 ** -10,
+                                           3 * 2.0 ** -10], np.float32)])
+    fp8 = rq.integers(0, 256, (64, 64)).astype(np.uint8)
+    fp8[(fp8 & 0x7F) == 0x7F] = 0x7E                             # no NaN codes
+    sc = rq.integers(100, 140, (64, 2)).astype(np.uint8)
+    np.savez_compressed(os.path.join(HERE, "e4m3.npz"), table=_e4m3_table(), x=xq, bytes=f32_to_e4m3(xq),
+                        fp8=fp8, scale=sc, dequant=dequantize_rowblock(fp8, sc).astype(np.float32))
     print("wrote fixtures to", HERE)
 
 

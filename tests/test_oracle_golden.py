@@ -164,3 +164,32 @@ def test_polar_express_orthogonalises_better_than_keller_in_five_steps():
         p6 = err(muon_ref.ns_fp32(W, 6, muon_ref.PE_SCHEDULE))
         assert p5 < k5, (M, N, p5, k5)
         assert p6 <= p5 * 1.05, (M, N, p6, p5)
+
+
+def test_e4m3_oracle_against_the_reference_host_helpers():
+    """oracle/quant_ref.py against fixtures recorded from ancora/kernels/quant.py's host code: the
+    decode table bit for bit; the rounding equal to f32_to_e4m3 wherever the input is not an exact
+    tie (the host helper sends ties to the smaller magnitude, the device conversion the kernels use
+    is round-to-nearest-even, which the oracle follows: at a tie it must pick the even one of the
+    two neighbours); the block dequantisation equal to dequantize_rowblock."""
+    from oracle import quant_ref
+    g = np.load(os.path.join(G, "e4m3.npz"))
+    tab = quant_ref.e4m3_table()
+    assert np.array_equal(np.nan_to_num(tab.astype(np.float32), nan=-7.0), np.nan_to_num(g["table"], nan=-7.0))
+    x, ref = g["x"], g["bytes"]
+    got = quant_ref._e4m3_rne(np.clip(x, -448.0, 448.0))          # the host helper saturates at 448
+    pos = tab[:127]
+    ax = np.minimum(np.abs(x).astype(np.float64), 448.0)
+    hi = np.clip(np.searchsorted(pos, ax), 1, 126)
+    lo = hi - 1
+    tie = (ax - pos[lo]) == (pos[hi] - ax)
+    assert tie.sum() > 100 and (~tie).sum() > 1000
+    same = (got & 0x7F) == (ref & 0x7F)
+    assert same[~tie].all()
+    assert np.array_equal(got & 0x80, ref & 0x80)                  # signs, signed zero included
+    even = np.where(lo % 2 == 0, lo, hi)
+    assert np.array_equal((got & 0x7F)[tie], even[tie].astype(np.uint8))
+    # dequantisation: the reference lays blocks along the last axis, the weight form along axis 0
+    want = g["dequant"]
+    mine = quant_ref.dequant_mxfp8_w(np.ascontiguousarray(g["fp8"].T), np.ascontiguousarray(g["scale"].T)).T
+    assert np.array_equal(mine.astype(np.float32), want)
