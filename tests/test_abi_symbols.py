@@ -41,3 +41,25 @@ def test_no_gpu_calls_fail_with_status_not_crash():
     # argument validation happens before any CUDA call
     assert l.anc_adamw_step(None, None, 0, 0, 0, None) == _lib.E_INVALID
     assert b"NULL" in l.anc_last_error()
+
+
+def test_product_never_reaches_the_oracle_or_torch():
+    """The package is the product: it must not import the CPU oracle (test infrastructure), torch,
+    triton or anything under a scratch folder, in any of its modules."""
+    pkg = os.path.join(ROOT, "ancora_cutile_b200")
+    bad = re.compile(r"^\s*(from|import)\s+(oracle|torch|triton|_work)\b", re.M)
+    for fn in sorted(os.listdir(pkg)):
+        if fn.endswith(".py"):
+            assert not bad.search(open(os.path.join(pkg, fn)).read()), fn
+    for fn in sorted(os.listdir(os.path.join(pkg, "csrc"))):
+        src = open(os.path.join(pkg, "csrc", fn)).read()
+        assert "oracle" not in src and "torch" not in src, fn
+
+
+def test_missing_library_is_an_error_not_a_fallback(tmp_path, monkeypatch):
+    """With no built library the loader raises; nothing computes on the host instead."""
+    import pytest
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libancora_b200.so"))
+    monkeypatch.setattr(_lib, "_lib", None)
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
