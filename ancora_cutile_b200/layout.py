@@ -117,3 +117,26 @@ class ArenaLayout:
             return 0, unit[1], unit[2] - unit[1]
         g = self.gmap[unit[1]]
         return 1, g["base"] + self.rank * g["per"] + unit[2] * g["elems"], unit[3] * g["elems"]
+
+    def exchange_schedule(self, unit_groups):
+        """Interleaving of this rank's units with the per-group collectives of the overlapped
+        exchange.  ``unit_groups[i]`` names the arena group of unit i ("adamw" or a shape key), in
+        execution order.  Returns a list of ("compute", i) and ("gather", group) steps in which
+
+          * every arena group -- the AdamW arena, then every shape group by descending size -- is
+            gathered exactly once, in that order on every rank (a collective must be entered by
+            all ranks in the same order, whether or not a rank owns anything of the group, and
+            however many units its share was cut into);
+          * a group's gather follows the last of this rank's units of that group.
+        """
+        order = ["adamw"] + [g["key"] for g in sorted(self.groups, key=lambda g: -g["total"])]
+        steps, done = [], 0
+        for grp in order:
+            idx = [i for i, k in enumerate(unit_groups) if k == grp]
+            if idx:
+                assert idx[0] >= done, "units must come in arena-group order"
+                steps += [("compute", i) for i in range(done, idx[-1] + 1)]
+                done = idx[-1] + 1
+            steps.append(("gather", grp))
+        assert done == len(unit_groups), "a unit names an unknown arena group"
+        return steps

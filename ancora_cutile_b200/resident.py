@@ -246,18 +246,28 @@ class ResidentHybrid:
                 L.check(L.lib().anc_stream_create(self.ctx.handle, C.byref(st)))
                 self._comm_stream = st.value
             cs = self._comm_stream
-            evs = self._events(len(self.units) + 1)
+            if getattr(self, "_overlap_for", None) is not self.units:
+                self._overlap_steps = self.layout.exchange_schedule(
+                    ["adamw" if u[0] == "adamw" else u[4] for u in self.units])
+                self._overlap_for = self.units
+            steps = self._overlap_steps
+            evs = self._events(sum(1 for op in steps if op[0] == "gather") + 1)
             lib = L.lib()
-            for u, ev in zip(self.units, evs):
-                self._compute_unit(u, si)
+            k = 0
+            for op, what in steps:
+                if op == "compute":
+                    self._compute_unit(self.units[what], si)
+                    continue
+                ev = evs[k]
+                k += 1
                 ev.record(si)
                 L.check(lib.anc_stream_wait_event(cs, ev.handle))
-                if u[0] == "adamw":
+                if what == "adamw":
                     self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, cs)
                 else:
-                    g = self._gmap[u[4]]
+                    g = self._gmap[what]
                     self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], cs)
-            done = evs[len(self.units)]
+            done = evs[k]
             done.record(cs)
             L.check(lib.anc_stream_wait_event(si, done.handle))
             return

@@ -141,3 +141,94 @@ def test_two_gloo_ranks_exchange_complementary_spans():
             r = b["rank"]
             mine = [(o, n) for (arena, o, n) in b["spans"] if arena == 1 and base <= o < base + 2 * per]
             assert _tiles(mine, base + r * per, base + r * per + counts[r] * e), (key, r)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_every_rank_enters_the_same_collectives_in_the_same_order(world):
+    """A small model whose groups do not divide evenly (one group has fewer matrices than ranks at
+    world 8) and a scratch cap that cuts shares into different numbers of units per rank: the
+    gather sequence is the same on every rank, once per arena group, after the rank's own units."""
+    shp = S.qwen3_0_6b_shapes(n_layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=4096)
+    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    seqs = []
+    for r in range(world):
+        lay = ArenaLayout(shp, mu, r, world)
+        caps = {g["key"]: 1 for g in lay.groups}                  # one matrix per unit
+        units = lay.make_units(caps)
+        names = ["adamw" if u[0] == "adamw" else u[1] for u in units]
+        steps = lay.exchange_schedule(names)
+        assert [i for op, i in steps if op == "compute"] == list(range(len(units)))
+        gathers = [g for op, g in steps if op == "gather"]
+        assert len(gathers) == 1 + len(lay.groups) and len(set(gathers)) == len(gathers)
+        for i, n in enumerate(names):                              # a unit precedes its group's gather
+            assert steps.index(("compute", i)) < steps.index(("gather", n))
+        seqs.append(gathers)
+    assert all(s == seqs[0] for s in seqs)
+    if world == 8:                                                 # some rank really owns nothing of a group
+        lays = [ArenaLayout(shp, mu, r, world) for r in range(world)]
+        assert any(len(g["names"][l.rank]) == 0 for l in lays for g in l.groups)
+
+
+def test_overlapped_step_issues_that_schedule(monkeypatch):
+    """The engine's overlapped-exchange branch, driven on the CPU with stand-ins for the device
+    calls: two ranks whose shares are cut into different numbers of units record the same
+    all-gather sequence (pointer offsets and counts included), each gather after an event wait."""
+    from ancora_cutile_b200 import resident
+
+    shp = S.qwen3_0_6b_shapes(n_layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=4096)
+    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+
+    class Ev:
+        def __init__(self, log):
+            self.log, self.handle = log, id(self)
+
+        def record(self, stream):
+            self.log.append(("record", stream))
+
+    class Lib:
+        def __init__(self, log):
+            self.log = log
+
+        def anc_stream_wait_event(self, stream, handle):
+            self.log.append(("wait", stream))
+            return 0
+
+    class Comm:
+        def __init__(self, log):
+            self.log = log
+
+        def allgather_bf16(self, ptr, per, stream):
+            self.log.append(("gather", ptr, per, stream))
+
+    class Buf:
+        def __init__(self, ptr):
+            self.ptr = ptr
+
+    logs = []
+    for r in range(2):
+        log = []
+        lay = ArenaLayout(shp, mu, r, 2)
+        eng = resident.ResidentHybrid.__new__(resident.ResidentHybrid)
+        eng.ctx, eng.world, eng.rank, eng.t = None, 2, r, 0
+        eng.layout, eng._gmap, eng.a_per = lay, lay.gmap, lay.a_per
+        eng.comm, eng.p2p, eng.nccl_overlap, eng._comm_stream = Comm(log), None, True, 77
+        eng.a_p16, eng.m_p16 = Buf(1 << 40), Buf(1 << 41)
+        caps = {g["key"]: (2 if r == 0 else 3) for g in lay.groups}        # different cuts per rank
+        eng.units = [("adamw", None, u[1], u[2]) if u[0] == "adamw" else ("muon", 0, u[2], u[3], u[1])
+                     for u in lay.make_units(caps)]
+        eng._compute_unit = lambda u, si, log=log: log.append(("compute", u[0], si))
+        eng._events = lambda n, log=log: [Ev(log) for _ in range(n)]
+        monkeypatch.setattr(resident.L, "lib", lambda log=log: Lib(log))
+        eng.step(5)
+        assert eng.t == 1
+        assert sum(1 for e in log if e[0] == "compute") == len(eng.units)
+        for i, e in enumerate(log):
+            if e[0] == "gather":                       # record on the compute stream, wait on the comm stream
+                assert log[i - 2] == ("record", 5) and log[i - 1] == ("wait", 77) and e[3] == 77
+        assert log[-2:] == [("record", 77), ("wait", 5)]  # the step ends ordered after the last gather
+        logs.append([e for e in log if e[0] == "gather"])
+    assert logs[0] == logs[1]
+    lay = ArenaLayout(shp, mu, 0, 2)
+    want = [((1 << 40), lay.a_per)] + [((1 << 41) + g["base"] * 2, g["per"])
+                                       for g in sorted(lay.groups, key=lambda g: -g["total"])]
+    assert [(e[1], e[2]) for e in logs[0]] == want
