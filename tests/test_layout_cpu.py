@@ -232,3 +232,49 @@ def test_overlapped_step_issues_that_schedule(monkeypatch):
     want = [((1 << 40), lay.a_per)] + [((1 << 41) + g["base"] * 2, g["per"])
                                        for g in sorted(lay.groups, key=lambda g: -g["total"])]
     assert [(e[1], e[2]) for e in logs[0]] == want
+
+
+def test_random_models_keep_the_layout_invariants():
+    """Property test over random small models (any number of matrices per shape, fewer matrices
+    than ranks included, AdamW tensors of ragged sizes) and world sizes 1..8."""
+    from hypothesis import given, settings, strategies as st
+
+    dims = st.sampled_from([128, 256, 384, 512])
+    model = st.tuples(
+        st.lists(st.tuples(dims, dims), min_size=0, max_size=14),          # Muon matrices (K, N)
+        st.lists(st.integers(1, 5000), min_size=1, max_size=6),            # AdamW tensor sizes
+        st.integers(1, 8),                                                 # world
+        st.sampled_from([None, 1, 3]),                                     # scratch cap
+        st.sampled_from([None, 1 << 16]),                                  # host chunk
+    )
+
+    @settings(max_examples=120, deadline=None)
+    @given(model)
+    def check(m):
+        mats, vecs, world, cap, chunk = m
+        shp = {f"v{i}": (n,) for i, n in enumerate(vecs)}
+        shp.update({f"layers.{i}.q_proj": s for i, s in enumerate(mats)})
+        mu = [n for n in shp if len(shp[n]) == 2]
+        lays = [ArenaLayout(shp, mu, r, world) for r in range(world)]
+        a = lays[0]
+        assert _tiles([(l.a_begin, l.a_end - l.a_begin) for l in lays], 0, a.a_padded)
+        for n in shp:
+            got = [l.owned_range(n) for l in lays]
+            assert _tiles([(s, e - s) for s, e in got if e > s], 0, _numel(shp[n])), n
+        gathers = []
+        for l in lays:
+            caps = None if cap is None else {g["key"]: cap for g in l.groups}
+            units = l.make_units(caps, chunk)
+            spans = {0: [], 1: []}
+            for u in units:
+                arena, off, n = l.unit_span(u)
+                spans[arena].append((off, n))
+            assert _tiles(spans[0], l.a_begin, l.a_end)
+            own = sum(_numel(shp[n]) for n in mu if l.m_owner[n] == l.rank)
+            assert sum(n for _, n in spans[1]) == own
+            assert len({o for o, _ in spans[1]}) == len(spans[1])
+            steps = l.exchange_schedule(["adamw" if u[0] == "adamw" else u[1] for u in units])
+            gathers.append([g for op, g in steps if op == "gather"])
+        assert all(g == gathers[0] for g in gathers) and len(gathers[0]) == 1 + len(a.groups)
+
+    check()
