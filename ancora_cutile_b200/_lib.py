@@ -106,13 +106,7 @@ SIGNATURES = {
     "anc_comm_destroy": (_i, [_vp]),
     "anc_comm_allgather_bf16": (_i, [_vp, _vp, _u64, _vp]),
     "anc_comm_reduce_scatter_grads": (_i, [_vp, _vp, _u64, _i, _vp]),
-    "anc_comm_bcast_segments": (_i, [_vp, _pp, C.POINTER(_u64), C.POINTER(_i), _i, _vp]),
     "anc_comm_barrier": (_i, [_vp, _vp]),
-    "anc_ipc_export_mem": (_i, [_vp, _vp, _vp]),
-    "anc_ipc_open_mem": (_i, [_vp, _vp, _pp]),
-    "anc_ipc_close_mem": (_i, [_vp, _vp]),
-    "anc_p2p_signal": (_i, [_vp, _vp, C.c_uint32, _vp]),
-    "anc_p2p_wait_flags": (_i, [_vp, _vp, _i, _i, C.c_uint32, _vp]),
 }
 
 _lib = None

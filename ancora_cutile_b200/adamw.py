@@ -26,14 +26,6 @@ _GRAD = {"bf16": L.GRAD_BF16, "f32": L.GRAD_F32}
 _ROUND = {"rne": L.ROUND_RNE, "sr": L.ROUND_SR}
 
 
-def _pick_otm(R):
-    """Kept for API parity (adamw.py:44-48); the multi-tensor kernel does not tile by it."""
-    for cand in (128, 64, 32, 16, 8, 4, 2):
-        if R % cand == 0:
-            return cand
-    return 1
-
-
 def step_scalars(lr, b1, b2, eps, t):
     """float32 scalars of step t, materialised once: 1-beta is the float32 subtraction the
     reference kernel performs (adamw.py:34-35), the bias corrections are computed in

@@ -17,8 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libancora_b200.so")
-SOURCES = ["runtime.cu", "adamw.cu", "muon_elem.cu", "ns_gemm.cu", "muon_plan.cu", "grad_prod.cu", "zero1.cu",
-           "p2p.cu"]
+SOURCES = ["runtime.cu", "adamw.cu", "muon_elem.cu", "ns_gemm.cu", "muon_plan.cu", "grad_prod.cu", "zero1.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--ftz=false", "--prec-div=true",
               "--prec-sqrt=true", "--fmad=true"]

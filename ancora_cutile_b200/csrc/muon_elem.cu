@@ -588,8 +588,9 @@ int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int
     ANC_CUDA(cudaStreamSynchronize(ctx->stream));
     if (ctx->d_work) cudaFree(ctx->d_work);
     ctx->d_work = nullptr;
+    ctx->work_bytes = 0;          // stays 0 if the allocation fails, so the next call retries
+    ANC_CUDA(cudaMalloc(&ctx->d_work, total * sizeof(float) * 2));
     ctx->work_bytes = total * sizeof(float) * 2;
-    ANC_CUDA(cudaMalloc(&ctx->d_work, ctx->work_bytes));
   }
   int grid = (int)(total < (size_t)ctx->sm_count * 8 ? total : (size_t)ctx->sm_count * 8);
   fro_partial_kernel<<<grid, kThreads, 0, st>>>(X, (float *)ctx->d_work, (int)total);
@@ -726,7 +727,20 @@ int anc_fro_normalize_static(int device, uint16_t *X, float *recip, int E, int M
               "anc_fro_normalize_static: %zu blocks of %d elements exceed the built-in scratch of %d "
               "blocks (E*M*N <= 2^30 elements); use anc_fro_normalize",
               total, kFroBlock, ANC_FRO_STATIC_MAX_BLOCKS);
-  anc_device_guard guard(device);
+  int n_dev = 0;
+  ANC_CUDA(cudaGetDeviceCount(&n_dev));
+  ANC_REQUIRE(device < n_dev, "device %d does not exist (%d visible)", device, n_dev);
+  // The kernels below must run on `device`: its scratch address is meaningless elsewhere.
+  // So the switch is checked here instead of being left to a guard that ignores a failure.
+  int prev_dev = -1;
+  ANC_CUDA(cudaGetDevice(&prev_dev));
+  if (prev_dev != device) ANC_CUDA(cudaSetDevice(device));
+  struct Restore {
+    int prev, cur;
+    ~Restore() {
+      if (prev != cur) cudaSetDevice(prev);
+    }
+  } restore = {prev_dev, device};
   StaticScratch sc;
   {
     std::lock_guard<std::mutex> lock(g_static_mu);

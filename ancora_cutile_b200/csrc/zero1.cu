@@ -17,10 +17,7 @@ struct NcclApi {
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
-  ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
-  ncclResult_t (*GroupStart)() = nullptr;
-  ncclResult_t (*GroupEnd)() = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 NcclApi g_nccl;
@@ -72,11 +69,8 @@ int anc_nccl_load(const char *path) {
             load_sym(g_nccl.CommInitRank, "ncclCommInitRank") &&
             load_sym(g_nccl.CommDestroy, "ncclCommDestroy") &&
             load_sym(g_nccl.AllGather, "ncclAllGather") &&
-            load_sym(g_nccl.Broadcast, "ncclBroadcast") &&
             load_sym(g_nccl.ReduceScatter, "ncclReduceScatter") &&
             load_sym(g_nccl.AllReduce, "ncclAllReduce") &&
-            load_sym(g_nccl.GroupStart, "ncclGroupStart") &&
-            load_sym(g_nccl.GroupEnd, "ncclGroupEnd") &&
             load_sym(g_nccl.GetErrorString, "ncclGetErrorString");
   if (!ok) {
     anc_set_error("NCCL library lacks a required symbol");
@@ -159,27 +153,6 @@ int anc_comm_reduce_scatter_grads(anc_comm *c, void *arena, uint64_t elems_per_r
   const ncclDataType_t dt = grad_dtype == ANC_GRAD_BF16 ? (ncclDataType_t)9 /* ncclBfloat16 */ : ncclFloat32;
   ANC_NCCL(g_nccl.ReduceScatter(arena, (char *)arena + (size_t)c->rank * elems_per_rank * esz,
                                 (size_t)elems_per_rank, dt, ncclSum, c->comm, st));
-  return ANC_OK;
-}
-
-int anc_comm_bcast_segments(anc_comm *c, uint16_t *const *ptr, const uint64_t *elems, const int *root,
-                            int n_segments, void *stream) {
-  ANC_REQUIRE(c && (n_segments == 0 || (ptr && elems && root)), "NULL argument");
-  anc_device_guard guard(c->ctx->device);
-  cudaStream_t st = anc_pick_stream(c->ctx, stream);
-  for (int i = 0; i < n_segments; ++i)
-    ANC_REQUIRE(root[i] >= 0 && root[i] < c->world && ptr[i], "segment %d: bad root or pointer", i);
-  ANC_NCCL(g_nccl.GroupStart());
-  for (int i = 0; i < n_segments; ++i) {
-    if (elems[i] == 0) continue;
-    ncclResult_t r =
-        g_nccl.Broadcast(ptr[i], ptr[i], (size_t)elems[i] * 2, ncclUint8, root[i], c->comm, st);
-    if (r != ncclSuccess) {
-      g_nccl.GroupEnd();
-      return nccl_fail(r, "ncclBroadcast");
-    }
-  }
-  ANC_NCCL(g_nccl.GroupEnd());
   return ANC_OK;
 }
 

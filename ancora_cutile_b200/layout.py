@@ -83,14 +83,13 @@ class ArenaLayout:
             return (lo - o, hi - o) if lo < hi else (0, 0)
         return (0, n) if self.m_owner[name] == self.rank else (0, 0)
 
-    def make_units(self, batch_cap=None, max_elems=None, halve_from=None):
+    def make_units(self, batch_cap=None, max_elems=None):
         """Units in execution order: ("adamw", begin, end) over arena-0 elements, then
         ("muon", group key, first, count) over this rank's matrices of each shape group, groups
         by descending size (the last unit's exchange or copy-out is the one nothing overlaps,
         so the smallest goes last).  ``batch_cap[key]`` bounds a Muon unit by the scratch batch
         of the plan; ``max_elems`` cuts units into sub-ranges of at most that many elements (host
-        pipelining); ``halve_from`` cuts a group with at least that many matrices of this rank in
-        two, so that the first half's exchange starts while the second half computes."""
+        pipelining)."""
         units = []
         if max_elems is None:
             units.append(("adamw", self.a_begin, self.a_end))
@@ -104,8 +103,6 @@ class ArenaLayout:
                 continue
             cap = mine if batch_cap is None else batch_cap[g["key"]]
             per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
-            if halve_from is not None and mine >= halve_from:
-                per = min(per, -(-mine // 2))
             for first in range(0, mine, per):
                 units.append(("muon", g["key"], first, min(per, mine - first)))
         return units

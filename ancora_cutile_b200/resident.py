@@ -37,13 +37,12 @@ def _numel(shape):
 
 class ResidentHybrid:
     def __init__(self, params, muon_names, no_decay_names=(), adamw_kw=None, muon_kw=None,
-                 grad_dtype="bf16", rounding="sr", seed=0, rank=0, world=1, comm=None, p2p=None,
+                 grad_dtype="bf16", rounding="sr", seed=0, rank=0, world=1, comm=None,
                  schedule=_UNSET, max_batch=0, ctx=None):
         """params: {name: fp32 ndarray} (every rank passes the same dict).
         comm: zero1.Comm; the updated bf16 parameters are exchanged with one NCCL all-gather per
         unit, issued on a second stream as soon as the unit is computed (``nccl_overlap``; set it
-        to False for plain all-gathers after the step).  p2p: True to prepare the experimental
-        copy-engine exchange instead (finish with ``connect_p2p``)."""
+        to False for plain all-gathers after the step)."""
         self.ctx = ctx or get_context()
         self.rank, self.world, self.comm = int(rank), int(world), comm
         self.grad_dtype, self.rounding, self.seed = grad_dtype, rounding, int(seed)
@@ -134,18 +133,6 @@ class ResidentHybrid:
         self._pin_w = None
         self._streams = None
         self._comm_stream = None
-        self.p2p = None
-        if p2p and W > 1:
-            from .zero1 import P2PExchange
-            self.p2p = P2PExchange(c, R, W, [self.a_p16.ptr, self.m_p16.ptr])
-            self.units = self._make_units(None, halve_from=8)
-
-    # ---------------------------------------------------------------- exchange set-up
-    def p2p_handles(self):
-        return self.p2p.local_handles()
-
-    def connect_p2p(self, all_handles):
-        self.p2p.connect(all_handles)
 
     # ---------------------------------------------------------------- locations
     def _loc(self, name):
@@ -171,15 +158,13 @@ class ResidentHybrid:
             return (lo - o, hi - o) if lo < hi else (0, 0)
         return (0, n) if self.m_owner[name] == self.rank else (0, 0)
 
-    def _make_units(self, max_elems, halve_from=None):
+    def _make_units(self, max_elems):
         """AdamW first, then shape groups by descending size (the last unit's exchange or
         copy-out is the one nothing overlaps, so the smallest goes last).  ``max_elems`` cuts
-        units into sub-ranges of at most that many elements (host pipelining); ``halve_from``
-        cuts a group with at least that many matrices of this rank in two, so that the first
-        half's exchange starts while the second half computes."""
+        units into sub-ranges of at most that many elements (host pipelining)."""
         units = []
         caps = {key: cap for key, (_, cap) in self._pgroup.items()}
-        for u in self.layout.make_units(caps, max_elems, halve_from):
+        for u in self.layout.make_units(caps, max_elems):
             if u[0] == "muon":
                 units.append(("muon", self._pgroup[u[1]][0], u[2], u[3], u[1]))
             elif max_elems is None:
@@ -225,20 +210,10 @@ class ResidentHybrid:
 
     def step(self, si=None, exchange=True):
         """One optimizer step on stream ``si``; asynchronous.  With world > 1 the updated bf16
-        parameters are exchanged: unit by unit over copy engines when the P2P exchange is
-        connected (overlapping the following units' compute), else by NCCL all-gathers."""
+        parameters are exchanged by NCCL all-gathers, one per arena group."""
         si = si or self.ctx.stream
         self.t += 1
         multi = exchange and self.world > 1
-        if multi and self.p2p is not None:
-            evs = self._events(len(self.units))
-            for u, ev in zip(self.units, evs):
-                self._compute_unit(u, si)
-                ev.record(si)
-                arena, off, n = self.unit_span(u)
-                self.p2p.push(arena, off * 2, n * 2, ev)
-            self.p2p.finish(si)
-            return
         if multi and self.nccl_overlap:
             # NCCL all-gather of each unit on a second stream as soon as the unit is computed
             if self._comm_stream is None:
@@ -348,9 +323,7 @@ class ResidentHybrid:
         step: AdamW's step number and scalars come from device memory (a schedule for the next
         ``horizon`` steps is uploaded here), everything else in the step has fixed arguments.
         Call after at least one eager ``step`` (first calls allocate); hyper-parameters are
-        frozen into the graph; the copy-engine exchange is not capturable (its sequence numbers
-        are launch arguments), the NCCL exchange is."""
-        assert self.p2p is None, "graph replay is not available with the copy-engine exchange"
+        frozen into the graph."""
         si = si or self.ctx.stream
         a = self.adamw_kw
         self.ctx.sync(si)
@@ -487,17 +460,11 @@ class ResidentHybrid:
             L.check(lib.anc_stream_wait_event(si, ev_in[k].handle))
             self._compute_unit(u, si)
             ev_c[k].record(si)
-            if multi and self.p2p is not None:
-                arena, off, n = self.unit_span(u)
-                self.p2p.push(arena, off * 2, n * 2, ev_c[k])
             L.check(lib.anc_stream_wait_event(s_out, ev_c[k].handle))
             d2h += self._d2h_unit(u, s_out)
             ev_out[k].record(s_out)
         if multi:
-            if self.p2p is not None:
-                self.p2p.finish(si)
-            else:
-                self.exchange(si)
+            self.exchange(si)
         for k in range(nu):
             L.check(lib.anc_stream_wait_event(si, ev_out[k].handle))
         self.ctx.sync(si)
@@ -583,9 +550,6 @@ class ResidentHybrid:
         if getattr(self, "_graph", None):
             L.lib().anc_graph_destroy(self._graph)
             self._graph = None
-        if self.p2p is not None:
-            self.p2p.destroy()
-            self.p2p = None
         self.adamw.free()
         for pl in self._sub_plans:
             pl.free()

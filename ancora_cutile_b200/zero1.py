@@ -127,94 +127,3 @@ class Comm:
         if self.handle:
             L.lib().anc_comm_destroy(self.handle)
             self.handle = None
-
-
-class P2PExchange:
-    """All-gather of arena slices by copy-engine pushes into IPC-mapped peer arenas.
-
-    Every rank owns two device arenas (bf16 AdamW parameters, bf16 Muon parameters) and a flag
-    array of ``world`` counters.  ``local_handles()`` gives the three 64-byte IPC handles to
-    hand to the other ranks; ``connect(all_handles)`` maps theirs.  ``push(arena, offset, bytes,
-    after)`` copies this rank's bytes to the same offset of every peer on per-peer streams
-    (so the copies run on separate copy engines) once event ``after`` has fired, then raises
-    this rank's flag on each peer.  ``finish(stream)`` makes ``stream`` wait until all peers'
-    pushes of the current step have landed here (bounded spin) and this rank's own pushes have
-    drained.  No SM is used for the payload, so the transfer overlaps the GEMMs.
-    """
-
-    def __init__(self, ctx, rank, world, arena_ptrs):
-        from .buffers import DBuf, Event
-        import numpy as np
-        self.ctx, self.rank, self.world = ctx, int(rank), int(world)
-        self.local = list(arena_ptrs)
-        self.flags = DBuf.zeros((64,), np.uint32, ctx)
-        self.seq = 0
-        self.peer = {}
-        self.streams = {}
-        self._events = {}
-        self._Event = Event
-        for p in range(self.world):
-            if p != self.rank:
-                s = C.c_void_p()
-                L.check(L.lib().anc_stream_create(ctx.handle, C.byref(s)))
-                self.streams[p] = s.value
-                self._events[p] = Event()
-
-    def local_handles(self):
-        out = []
-        for ptr in self.local + [self.flags.ptr]:
-            buf = (C.c_char * 64)()
-            L.check(L.lib().anc_ipc_export_mem(self.ctx.handle, ptr, buf))
-            out.append(bytes(buf))
-        return out
-
-    def connect(self, all_handles):
-        """all_handles[r] = rank r's ``local_handles()``."""
-        for p in range(self.world):
-            if p == self.rank:
-                continue
-            ptrs = []
-            for h in all_handles[p]:
-                q = C.c_void_p()
-                L.check(L.lib().anc_ipc_open_mem(self.ctx.handle, (C.c_char * 64).from_buffer_copy(h), C.byref(q)))
-                ptrs.append(q.value)
-            self.peer[p] = ptrs
-
-    def begin_step(self):
-        pass
-
-    def push(self, arena, offset_bytes, nbytes, after_event):
-        """Arena index (0 or 1), byte offset of this rank's slice, its size."""
-        self.seq = (self.seq + 1) & 0xFFFFFFFF
-        lib = L.lib()
-        for p, st in self.streams.items():
-            L.check(lib.anc_stream_wait_event(st, after_event.handle))
-            if nbytes:
-                L.check(lib.anc_d2d(self.ctx.handle, self.peer[p][arena] + offset_bytes,
-                                    self.local[arena] + offset_bytes, nbytes, st))
-            L.check(lib.anc_p2p_signal(self.ctx.handle, self.peer[p][2] + 4 * self.rank, self.seq, st))
-        return self.seq
-
-    def wait_peers(self, stream, seq=None):
-        """``stream`` waits until every peer's push number ``seq`` (default: latest) has landed."""
-        L.check(L.lib().anc_p2p_wait_flags(self.ctx.handle, self.flags.ptr, self.world, self.rank,
-                                           self.seq if seq is None else seq, C.c_void_p(stream or None)))
-
-    def finish(self, stream):
-        self.wait_peers(stream)
-        for p, st in self.streams.items():
-            self._events[p].record(st)
-            L.check(L.lib().anc_stream_wait_event(C.c_void_p(stream or None), self._events[p].handle))
-
-    def destroy(self):
-        lib = L.lib()
-        for p, ptrs in self.peer.items():
-            for q in ptrs:
-                lib.anc_ipc_close_mem(self.ctx.handle, q)
-        self.peer = {}
-        for st in self.streams.values():
-            lib.anc_stream_destroy(self.ctx.handle, st)
-        self.streams = {}
-        if self.flags is not None:
-            self.flags.free()
-            self.flags = None

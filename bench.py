@@ -237,22 +237,15 @@ def main():
     anc.set_polar_express(True)
     params = S.synthetic_params(shp, seed=0)
     no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
-    # exchange of the updated bf16 parameters: "nccl_overlap" (default), "nccl" (after the step),
-    # "p2p" (experimental copy-engine pushes)
+    # exchange of the updated bf16 parameters: "nccl_overlap" (default) or "nccl" (after the step)
     xmode = os.environ.get("ANCORA_EXCHANGE", "nccl_overlap")
-    use_p2p = world > 1 and xmode == "p2p"
     eng = anc.ResidentHybrid(params, muon_names, no_decay_names=no_decay, adamw_kw=ADAMW_KW, muon_kw=MUON_KW,
                              grad_dtype="bf16", rounding="sr", seed=SEED_SR, rank=rank, world=world,
-                             comm=comm, p2p=use_p2p, schedule=anc.PE_SCHEDULE, ctx=ctx)
+                             comm=comm, schedule=anc.PE_SCHEDULE, ctx=ctx)
     del params
     eng.nccl_overlap = world > 1 and xmode == "nccl_overlap"
-    if use_p2p:
-        box = [None] * world
-        dist.all_gather_object(box, eng.p2p_handles())
-        eng.connect_p2p(box)
-    config["exchange"] = ("copy-engine pushes over NVLink (IPC), overlapped per unit" if use_p2p
-                          else ("NCCL all-gather per unit on a second stream" if eng.nccl_overlap
-                                else ("NCCL all-gather after the step" if world > 1 else "none")))
+    config["exchange"] = ("NCCL all-gather per unit on a second stream" if eng.nccl_overlap
+                          else ("NCCL all-gather after the step" if world > 1 else "none"))
     # synthetic bf16 gradients, written into the page-locked staging views and uploaded once
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)

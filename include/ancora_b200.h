@@ -330,24 +330,7 @@ ANC_API int anc_comm_allgather_bf16(anc_comm *comm, uint16_t *arena, uint64_t el
  * data-parallel replicas. */
 ANC_API int anc_comm_reduce_scatter_grads(anc_comm *comm, void *arena, uint64_t elems_per_rank,
                                           int grad_dtype, void *stream);
-/* Grouped broadcasts of variable segments: segment i (ptr[i], elems[i]) is sent
- * by root[i] to everybody. */
-ANC_API int anc_comm_bcast_segments(anc_comm *comm, uint16_t *const *ptr, const uint64_t *elems,
-                                    const int *root, int n_segments, void *stream);
 ANC_API int anc_comm_barrier(anc_comm *comm, void *stream);
-
-/* Copy-engine exchange over NVLink (no counterpart in the reference).  A rank exports its
- * arena (cudaMalloc'ed) as a 64-byte IPC handle; peers open it and push their slices into
- * it with anc_d2d on their own streams, then raise the receiver's flag with anc_p2p_signal
- * on the same stream.  anc_p2p_wait_flags launches a bounded wait for flags[i] >= value for
- * all i != skip (a wait that runs out sets status bit 0x10 and returns). */
-#define ANC_IPC_HANDLE_BYTES 64
-ANC_API int anc_ipc_export_mem(anc_ctx *ctx, void *dptr, void *handle64);
-ANC_API int anc_ipc_open_mem(anc_ctx *ctx, const void *handle64, void **peer_ptr);
-ANC_API int anc_ipc_close_mem(anc_ctx *ctx, void *peer_ptr);
-ANC_API int anc_p2p_signal(anc_ctx *ctx, uint32_t *remote_flag, uint32_t value, void *stream);
-ANC_API int anc_p2p_wait_flags(anc_ctx *ctx, const uint32_t *flags, int n, int skip, uint32_t value,
-                               void *stream);
 
 #ifdef __cplusplus
 }

@@ -80,25 +80,6 @@ def test_muon_zero_ns_steps_and_plain_momentum(ctx):
     opt.free()
 
 
-def test_peer_wait_runs_out_and_context_survives(ctx):
-    """A wait on a completion flag that nothing raises returns after its bound with status bit
-    0x10; the context stays usable afterwards (no trap, no hang)."""
-    lib = L.lib()
-    flags = anc.DBuf.zeros((64,), np.uint32, ctx)
-    L.check(lib.anc_p2p_wait_flags(ctx.handle, flags.ptr, 2, 0, 1, None))     # waits for flags[1] >= 1
-    ctx.sync()
-    assert ctx.status() == 0x10
-    assert ctx.status() == 0                                                   # reading clears it
-    # a raised flag is seen at once, and ordinary work still runs
-    flags.upload(np.array([0, 5] + [0] * 62, np.uint32))
-    L.check(lib.anc_p2p_wait_flags(ctx.handle, flags.ptr, 2, 0, 5, None))
-    x = anc.DBuf(np.arange(16, dtype=np.float32), ctx)
-    assert np.array_equal(x.to_numpy(), np.arange(16, dtype=np.float32))
-    ctx.sync()
-    assert ctx.status() == 0
-    flags.free(); x.free()
-
-
 def test_dbuf_views(ctx):
     """_DBuf semantics (ancora/model/resident.py:52-94): view shares memory, at_pos offsets by rows,
     a view must not be freed."""

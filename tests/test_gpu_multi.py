@@ -34,10 +34,8 @@ def _run_engine(rank, world, mode, ctx, comm=None, all_gather=None):
     mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
     nd = tuple(n for n, s in shp.items() if len(s) == 1)
     eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=3,
-                             rank=rank, world=world, comm=comm, p2p=(mode == "p2p"),
+                             rank=rank, world=world, comm=comm,
                              schedule=anc.PE_SCHEDULE, ctx=ctx)
-    if mode == "p2p":
-        eng.connect_p2p(all_gather(eng.p2p_handles()))
     for k in range(3):
         eng.upload_grads(S.synthetic_grads_bf16(shp, seed=20 + k), ctx.stream)
         eng.step(ctx.stream)
@@ -80,7 +78,7 @@ def _worker(rank, world, port, mode, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["p2p", "nccl"])
+@pytest.mark.parametrize("mode", ["nccl"])
 def test_two_ranks_hold_the_single_gpu_bits(mode):
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")

@@ -64,13 +64,13 @@ def test_layout_is_the_same_on_every_rank_and_partitions_everything(which, world
 
 @pytest.mark.parametrize("which", ["qwen3", "moe"])
 @pytest.mark.parametrize("world", [1, 2, 8])
-@pytest.mark.parametrize("mode", ["plain", "halved", "host_chunks", "capped"])
+@pytest.mark.parametrize("mode", ["plain", "host_chunks", "capped"])
 def test_units_cover_exactly_what_the_rank_owns(which, world, mode):
     shp, mu = _family(which)
     for r in range(world):
         lay = ArenaLayout(shp, mu, r, world)
         caps = {g["key"]: max(1, min(8, len(g["names"][r]))) for g in lay.groups} if mode == "capped" else None
-        units = lay.make_units(caps, 16 << 20 if mode == "host_chunks" else None, 8 if mode == "halved" else None)
+        units = lay.make_units(caps, 16 << 20 if mode == "host_chunks" else None)
         spans = {0: [], 1: []}
         for u in units:
             arena, off, n = lay.unit_span(u)
@@ -211,7 +211,7 @@ def test_overlapped_step_issues_that_schedule(monkeypatch):
         eng = resident.ResidentHybrid.__new__(resident.ResidentHybrid)
         eng.ctx, eng.world, eng.rank, eng.t = None, 2, r, 0
         eng.layout, eng._gmap, eng.a_per = lay, lay.gmap, lay.a_per
-        eng.comm, eng.p2p, eng.nccl_overlap, eng._comm_stream = Comm(log), None, True, 77
+        eng.comm, eng.nccl_overlap, eng._comm_stream = Comm(log), True, 77
         eng.a_p16, eng.m_p16 = Buf(1 << 40), Buf(1 << 41)
         caps = {g["key"]: (2 if r == 0 else 3) for g in lay.groups}        # different cuts per rank
         eng.units = [("adamw", None, u[1], u[2]) if u[0] == "adamw" else ("muon", 0, u[2], u[3], u[1])
