@@ -53,7 +53,8 @@ class Context:
         code = self.status()
         if code:
             raise L.AncoraError(L.E_DEVICE, f"device status word 0x{code:x} "
-                                "(1 TMA wait, 2 MMA wait, 4 epilogue wait ran out; 8 bad table index)")
+                                "(1 TMA wait, 2 MMA wait, 4 epilogue wait ran out; 8 bad table index; "
+                                "0x10 a tile's dependency never completed)")
 
     def flush_l2(self, stream=None):
         L.check(L.lib().anc_flush_l2(self.handle, C.c_void_p(stream or None)))

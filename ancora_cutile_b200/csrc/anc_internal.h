@@ -29,7 +29,7 @@ struct anc_upd_extra { uint8_t *fp8; uint8_t *scale; uint16_t *p16_t; uint8_t *f
 #define ANC_DEV_TIMEOUT_MMA 0x2u
 #define ANC_DEV_TIMEOUT_EPI 0x4u
 #define ANC_DEV_BAD_INDEX 0x8u       // a table index failed its bounds check
-#define ANC_DEV_TIMEOUT_PEER 0x10u   // a peer rank's completion flag never arrived
+#define ANC_DEV_TIMEOUT_DEP 0x10u    // a tile's dependency (the matrix's previous phase) never completed
 
 void anc_set_error(const char *fmt, ...);
 int anc_cuda_fail(cudaError_t e, const char *what);
@@ -75,8 +75,9 @@ int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int
 int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
                               int elems_per_w, int grad_dtype, float momentum, int nesterov,
                               float *partial, cudaStream_t st);
+// sched (nullable): 2 + E scheduler words of the chain kernel, cleared here
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
-                            float eps, cudaStream_t st);
+                            float eps, uint32_t *sched, cudaStream_t st);
 int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int E, int M, int N,
                            cudaStream_t st);
 int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_extras, const uint16_t *obase,
@@ -87,4 +88,10 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_ext
 int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
                        int E, int M, int N, float alpha, float beta, const float *mscale,
                        cudaStream_t st);
+// One persistent launch for the whole chain (M and N multiples of 256, at most 16 steps); the result is
+// in X for an even number of steps, in Y for an odd one.  sched: 2 + E zeroed words.
+bool anc_ns_chain_supported(const anc_ctx *ctx, int M, int N, int steps);
+int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uint16_t *B, int E, int M, int N,
+                        int steps, const float *coeffs, const float *mscale, uint32_t *sched,
+                        uint32_t spin_limit, cudaStream_t st);
 void anc_gemm_cache_destroy(anc_ctx *ctx);

@@ -218,10 +218,19 @@ momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int ti
 // thread-strided partial sums in index order, then the fixed tree.
 __global__ void __launch_bounds__(kThreads)
 fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip, int per_matrix,
-                    float eps) {
+                    float eps, uint32_t *sched) {
   __shared__ float wsum[kThreads / 32];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (sched != nullptr && threadIdx.x == 0) {
+    // scheduler words of the chain kernel that follows: tile counter, abort word, one
+    // completion counter per matrix
+    sched[2 + blockIdx.x] = 0u;
+    if (blockIdx.x == 0) {
+      sched[0] = 0u;
+      sched[1] = 0u;
+    }
+  }
   const float *pp = partial + (size_t)blockIdx.x * per_matrix;
   float acc = 0.f;
   for (int k = threadIdx.x; k < per_matrix; k += kThreads) acc = __fadd_rn(acc, pp[k]);
@@ -622,10 +631,10 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t s
 }
 
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
-                            float eps, cudaStream_t st) {
+                            float eps, uint32_t *sched, cudaStream_t st) {
   (void)ctx;
   if (E <= 0) return ANC_OK;
-  ANC_CUDA(launch_pdl(fro_finalize_kernel, E, st, partial, recip, per_matrix, eps));
+  ANC_CUDA(launch_pdl(fro_finalize_kernel, E, st, partial, recip, per_matrix, eps, sched));
   return ANC_OK;
 }
 

@@ -40,18 +40,29 @@ struct anc_muon_plan {
   uint16_t *X = nullptr, *Y = nullptr, *A = nullptr, *B = nullptr;
   float *recip = nullptr;
   float *partial = nullptr;       // per-tile sums of squares written by the momentum kernel
+  uint32_t *sched = nullptr;      // scheduler words of the chain kernel: 2 + largest batch
   uint64_t scratch_bytes = 0;
   bool timing = false;
   std::vector<TimedSpan> spans;
   double last_flops = 0.0;
+  double last_flops_executed = 0.0;
   int last_launches = 0;
 };
 
 // The chain on an UN-normalised X: the Frobenius factor r[e] = recip[e] enters through the
 // epilogues of the first iteration (A = r^2 X X^T, Y = (a r) X + r (B X)), which equals the
 // chain on r*X without ever writing r*X back to memory.
+// sched: the chain kernel's scheduler words (cleared by the Frobenius finalize kernel); when it
+// is NULL, or the shape is outside the chain kernel's reach, every phase is its own launch.
 static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16_t *&Y, int E, int M,
-                    int N, int steps, const float *coeffs, const float *recip, cudaStream_t st) {
+                    int N, int steps, const float *coeffs, const float *recip, uint32_t *sched,
+                    cudaStream_t st) {
+  if (sched && anc_ns_chain_supported(ctx, M, N, steps)) {
+    int rc = anc_launch_ns_chain(ctx, X, Y, A, B, E, M, N, steps, coeffs, recip, sched, 0, st);
+    if (rc) return rc;
+    if (steps & 1) std::swap(X, Y);
+    return ANC_OK;
+  }
   for (int k = 0; k < steps; ++k) {
     const float a = coeffs[3 * k], b = coeffs[3 * k + 1], c = coeffs[3 * k + 2];
     const float *ms = (k == 0) ? recip : nullptr;
@@ -73,7 +84,7 @@ static void plan_free(anc_muon_plan *pl) {
     if (g.d_ext) cudaFree(g.d_ext);
   }
   for (void *p : {(void *)pl->X, (void *)pl->Y, (void *)pl->A, (void *)pl->B, (void *)pl->recip,
-                  (void *)pl->partial})
+                  (void *)pl->partial, (void *)pl->sched})
     if (p) cudaFree(p);
   for (auto &s : pl->spans) {
     cudaEventDestroy(s.a);
@@ -188,6 +199,7 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->B, ae * 2);
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->recip, emax * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial, (xe / 4096) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sched, (emax + 2) * sizeof(uint32_t));
     if (e != cudaSuccess) {
       plan_free(pl);
       return anc_cuda_fail(e, "muon scratch");
@@ -248,18 +260,27 @@ int step_chunk(anc_muon_plan *pl, const ChunkRef &c, double lr, float momentum, 
   if (rc) return rc;
   begin_span(1);
   if (ns_steps > 0)   // 1/(||u||_F + eps) per matrix from the momentum kernel's tile sums
-    rc = anc_launch_fro_finalize(ctx, pl->partial, pl->recip, E, epw / 4096, eps, st);
+    rc = anc_launch_fro_finalize(ctx, pl->partial, pl->recip, E, epw / 4096, eps, pl->sched, st);
   else                // no iteration to fold the factor into: normalise in place
     rc = anc_launch_fro_normalize(ctx, X, pl->recip, E, g.M, g.Nn, eps, st);
   end_span();
   if (rc) return rc;
   begin_span(2);
-  rc = ns_chain(ctx, X, pl->A, pl->B, Y, E, g.M, g.Nn, ns_steps, coeffs, pl->recip, st);
+  rc = ns_chain(ctx, X, pl->A, pl->B, Y, E, g.M, g.Nn, ns_steps, coeffs, pl->recip, pl->sched, st);
   end_span();
   if (rc) return rc;
   pl->last_flops +=
       (double)E * ns_steps * (4.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M);
-  pl->last_launches += 3 * ns_steps;
+  // executed by the tensor cores: the symmetric phases compute the pair tiles on or below the
+  // diagonal only (mb2*(mb2+1)/2 of mb2^2 tiles of 256x256), the apply phase everything
+  {
+    const double nb = (g.M % 256 == 0) ? g.M / 256.0 : g.M / 128.0;   // tile rows: CTA-pair or single-CTA kernel
+    const double sym_frac = (nb + 1.0) / (2.0 * nb);
+    pl->last_flops_executed += (double)E * ns_steps *
+                               (sym_frac * (2.0 * g.M * (double)g.M * g.Nn + 2.0 * g.M * (double)g.M * g.M) +
+                                2.0 * g.M * (double)g.M * g.Nn);
+  }
+  pl->last_launches += (ns_steps > 0 && anc_ns_chain_supported(ctx, g.M, g.Nn, ns_steps)) ? 1 : 3 * ns_steps;
   begin_span(3);
   rc = anc_launch_update_group(ctx, g.d_upd + c.w0, g.d_ext ? (const void *)(g.d_ext + c.w0) : nullptr, X, E,
                                epw, scale_wide, scale_tall, st);
@@ -323,7 +344,7 @@ int anc_muon_plan_set_timing(anc_muon_plan *pl, int on) {
   return ANC_OK;
 }
 
-int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double *ns_flops, int *ns_launches) {
+int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double ns_flops[2], int *ns_launches) {
   ANC_REQUIRE(pl && ms, "NULL argument");
   anc_device_guard guard(pl->ctx->device);
   for (int i = 0; i < 4; ++i) ms[i] = 0.f;
@@ -333,7 +354,10 @@ int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double *ns_flops, 
     ANC_CUDA(cudaEventElapsedTime(&t, s.a, s.b));
     ms[s.phase] += t;
   }
-  if (ns_flops) *ns_flops = pl->last_flops;
+  if (ns_flops) {
+    ns_flops[0] = pl->last_flops;            // dense count: steps * (4 M^2 N + 2 M^3) per matrix
+    ns_flops[1] = pl->last_flops_executed;   // what the tensor cores ran (lower pair tiles only in the symmetric phases)
+  }
   if (ns_launches) *ns_launches = pl->last_launches;
   for (auto &s : pl->spans) {
     cudaEventDestroy(s.a);
@@ -341,6 +365,7 @@ int anc_muon_plan_last_timing(anc_muon_plan *pl, float ms[4], double *ns_flops, 
   }
   pl->spans.clear();
   pl->last_flops = 0.0;
+  pl->last_flops_executed = 0.0;
   pl->last_launches = 0;
   return ANC_OK;
 }
@@ -369,7 +394,9 @@ int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t
   if (steps == 0) return anc_launch_fro_normalize(ctx, X, recip, E, M, N, eps, st);
   // block sums of squares -> recip; the factor itself is applied inside the first iteration
   const size_t bpm = ((size_t)M * N) / 16384;
-  const size_t need = (size_t)E * bpm * sizeof(float);
+  // workspace: E * bpm partial sums, then the chain kernel's 2 + E scheduler words
+  const size_t sched_off = ((size_t)E * bpm * sizeof(float) + 255) / 256 * 256;
+  const size_t need = sched_off + ((size_t)E + 2) * sizeof(uint32_t);
   if (need > ctx->work_bytes) {
     ANC_CUDA(cudaStreamSynchronize(st));
     ANC_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -381,10 +408,11 @@ int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t
   }
   int rc = anc_launch_fro_partial(ctx, X, (float *)ctx->d_work, E, M, N, st);
   if (rc) return rc;
-  rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, eps, st);
+  uint32_t *sched = (uint32_t *)((char *)ctx->d_work + sched_off);
+  rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, eps, sched, st);
   if (rc) return rc;
   uint16_t *x = X, *y = Y;
-  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, st);
+  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, sched, st);
   if (rc) return rc;
   if (x != X)   // odd number of steps: result sits in Y, copy it home (muon_ns.py:274-276)
     ANC_CUDA(cudaMemcpyAsync(X, x, (size_t)E * M * N * 2, cudaMemcpyDeviceToDevice, st));

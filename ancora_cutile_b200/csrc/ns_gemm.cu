@@ -452,6 +452,21 @@ __device__ __forceinline__ void epi_bar(int id) {   // the 128 epilogue threads 
   asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
 }
 
+// Barrier of the 128 epilogue threads that also ORs a predicate, so that a decision taken on a
+// flag other roles may raise at any moment is the same for all of them.
+__device__ __forceinline__ bool epi_bar_or(int id, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %2, 0;\n\t"
+      "barrier.cta.red.or.pred q, %1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
 // tile_tab entries here are (I | J << 8) in units of 256 rows / 256 columns.
 __global__ void __launch_bounds__(kThreads, 1)
 ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -618,6 +633,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       epi_bar(2);                             // staging is free for this tile
       bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
       if (ok && p.mode != 0) ok = mbar_wait(dfull_bar, acc_it & 1, abort_flag);
+      ok = __all_sync(0xFFFFFFFFu, ok);       // the warp-wide TMEM loads below need a converged warp
       if (!ok) {
         if (lane == 0) atomicOr(p.status, ANC_DEV_TIMEOUT_EPI);
         *abort_flag = 1;
@@ -677,8 +693,8 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
         fence_async_smem();                   // staging writes visible to the TMA store
       }
-      epi_bar(1);                             // every row of the staging tile is final
-      if (*abort_flag) break;                 // uniform: the flag was set before the barrier
+      // every row of the staging tile is final; the abort decision is made uniform by the barrier
+      if (epi_bar_or(1, *abort_flag != 0)) break;
       if (elected) {
         for (int b = 0; b < 2 * nblk; ++b)
           tma_store_2d(&tmC, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
@@ -691,6 +707,448 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                // the peer's shared memory and barriers stay valid until here
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+
+// ====================================================================================
+// Whole Newton-Schulz chain in ONE persistent launch (CTA pairs as above).
+//
+// All 3 * steps phases of all E matrices form one tile queue, phase-major:
+//   [iteration 0: gram tiles of matrix 0..E-1 | poly tiles 0..E-1 | apply tiles 0..E-1 | iteration 1 ...]
+// CTA pairs claim tiles with an integer atomicAdd (dynamic scheduling: a pair that starts late,
+// or shares its SMs with another stream's kernel, simply takes fewer tiles).  A tile of matrix
+// e may start when every tile of e's previous phase has been stored, which is tracked by one
+// counter of completed half-tiles per matrix; the same rule makes the reuse of A, B and the
+// X/Y ping-pong buffers safe.  Tiles are claimed in queue order and only ever depend on
+// earlier tiles, so the smallest unfinished tile can always run: waiting cannot deadlock.
+// The tile -> output mapping and each tile's K order are those of the per-phase kernel, so
+// the results are bitwise the same.
+//
+// Roles (224 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-5
+// epilogue, warp 6 scheduler (leader CTA): it claims a tile, waits for the tile's
+// dependencies and publishes it to both CTAs through a small ring in shared memory.
+// Every wait is bounded; a wait that runs out raises the launch-wide abort word, and all
+// roles drain and return.
+// ====================================================================================
+constexpr int kChainThreads = 224;
+constexpr int kSchedSlots = 3;
+constexpr int kMaxChainSteps = 16;
+constexpr uint32_t kTileDone = 0xFFFFFFFFu;
+constexpr int kSmemBytes3 = kStages2 * kStageBytes2 + kEpiBytes + 1024 + 512;
+
+struct alignas(64) ChainMaps {
+  CUtensorMap xy128[2];   // the two ping-pong operand buffers, boxes of 64 columns x 128 rows
+  CUtensorMap xy64[2];    // the same buffers, boxes of 64 x 64 (N-major operand of the apply phase)
+  CUtensorMap a128, b128; // Gram matrix A and polynomial B, boxes of 64 columns x 128 rows
+};
+
+struct ChainParams {
+  uint16_t *A, *B;                     // plain pointers for the mirrored stores
+  const uint32_t *tab_sym, *tab_full;  // (I | J << 8) per local tile
+  const float *mscale;                 // per-matrix Frobenius factor folded into iteration 0 (nullable)
+  uint32_t *sched;                     // [0] next tile, [1] abort, [2 + e] completed half-tiles of matrix e
+  uint32_t *status;
+  int E, M, N, steps;
+  int g, a;                            // tiles per matrix in a symmetric phase / in the apply phase
+  uint32_t total_tiles;
+  uint32_t spin_limit;
+  float coef[3 * kMaxChainSteps];
+};
+
+struct ChainTile {
+  int k, mode, e, I, J;
+};
+
+__device__ __forceinline__ ChainTile chain_decode(const ChainParams &p, uint32_t t) {
+  const uint32_t per_it = (uint32_t)p.E * (2u * (uint32_t)p.g + (uint32_t)p.a);
+  ChainTile ti;
+  ti.k = (int)(t / per_it);
+  uint32_t r = t - (uint32_t)ti.k * per_it;
+  const uint32_t eg = (uint32_t)p.E * (uint32_t)p.g;
+  uint32_t per = (uint32_t)p.g;
+  ti.mode = 0;
+  if (r >= 2u * eg) {
+    r -= 2u * eg;
+    ti.mode = 2;
+    per = (uint32_t)p.a;
+  } else if (r >= eg) {
+    r -= eg;
+    ti.mode = 1;
+  }
+  ti.e = (int)(r / per);
+  const uint32_t l = r - (uint32_t)ti.e * per;
+  const uint32_t tt = (ti.mode == 2 ? p.tab_full : p.tab_sym)[l];
+  ti.I = (int)(tt & 0xFF);
+  ti.J = (int)((tt >> 8) & 0xFF);
+  return ti;
+}
+
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (the data it guards was written by the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                  uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    if (it > 64) {
+      __nanosleep(64);
+      if ((it & 255) == 0 && *abort_flag) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *ptr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(uint32_t *ptr, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+// Orders accesses made through the generic proxy (plain loads/stores, atomics) with accesses
+// made through the async proxy (TMA) by this thread.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kChainThreads, 1)
+ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ ChainParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gen_base = smem_raw + (base - raw);
+  const uint32_t epi_base = base + kStages2 * kStageBytes2;
+  uint8_t *epi_gen = gen_base + kStages2 * kStageBytes2;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_gen + kEpiBytes);
+  const uint32_t bar0 = epi_base + kEpiBytes;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + 2 + b); };
+  const uint32_t dfull_bar = bar0 + 8u * (2 * kStages2 + 4);
+  auto sfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 5 + s); };                 // tile published
+  auto sempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 5 + kSchedSlots + s); };  // slot read by all
+  constexpr int kNumBars = 2 * kStages2 + 5 + 2 * kSchedSlots;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile uint32_t *ring = reinterpret_cast<volatile uint32_t *>(tmem_slot + 2);
+  const uint32_t ring_addr = bar0 + 8u * kNumBars + 8u;
+  const uint32_t abort_addr = bar0 + 8u * kNumBars + 4u;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const uint32_t limit = p.spin_limit;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);
+    }
+    mbar_init(dfull_bar, 1);
+    for (int s = 0; s < kSchedSlots; ++s) {
+      mbar_init(sfull_bar(s), 1);
+      // readers of a slot: leader's producer, MMA issuer and 4 epilogue warps; peer's producer and 4 epilogue warps
+      mbar_init(sempty_bar(s), 11);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  // Raises the abort state everywhere: this CTA, the peer CTA, and the launch-wide word that
+  // the schedulers of the other pairs poll while they wait for a dependency.
+  auto raise_abort = [&](uint32_t bit) {
+    atomicOr(p.status, bit);
+    *abort_flag = 1;
+    st_cluster_u32(map_to_cta(abort_addr, crank ^ 1u), 1u);
+    atomicExch(&p.sched[1], 1u);
+  };
+  // Next tile of this role (n-th tile of the pair), or kTileDone.  The scheduler publishes a
+  // tile only after its dependency wait (bounded by p.spin_limit), so this wait uses the long
+  // fixed bound: it must outlast the scheduler's.
+  auto ring_get = [&](uint32_t n, bool arrive, uint32_t bit) -> uint32_t {
+    const int slot = (int)(n % kSchedSlots);
+    if (!mbar_wait_cluster(sfull_bar(slot), (n / kSchedSlots) & 1u, abort_flag, kSpinLimit)) {
+      if (!*abort_flag) raise_abort(bit);
+      return kTileDone;
+    }
+    const uint32_t t = ring[slot];
+    if (arrive) mbar_arrive_cluster(map_to_cta(sempty_bar(slot), 0));
+    return t;
+  };
+
+  if (warp == 6) {
+    // ------------------------------------------------------------ scheduler (leader only)
+    if (lane == 0 && crank == 0) {
+      const uint32_t per_e_it = 2u * (2u * (uint32_t)p.g + (uint32_t)p.a);   // half-tiles per matrix and iteration
+      for (uint32_t n = 0;; ++n) {
+        const int slot = (int)(n % kSchedSlots);
+        uint32_t t = kTileDone;
+        if (mbar_wait_cluster(sempty_bar(slot), ((n / kSchedSlots) & 1u) ^ 1u, abort_flag, kSpinLimit)) {
+          t = atomicAdd(&p.sched[0], 1u);
+          if (t >= p.total_tiles) t = kTileDone;
+        } else if (!*abort_flag) {
+          raise_abort(ANC_DEV_TIMEOUT_DEP);
+        }
+        if (t != kTileDone) {
+          const ChainTile ti = chain_decode(p, t);
+          const uint32_t need = (uint32_t)ti.k * per_e_it +
+                                (ti.mode == 1 ? 2u * (uint32_t)p.g : (ti.mode == 2 ? 4u * (uint32_t)p.g : 0u));
+          if (need) {
+            const uint32_t *cnt = p.sched + 2 + ti.e;
+            bool ready = false;
+            for (uint32_t it = 0; it < limit; ++it) {
+              if (ld_acquire_gpu(cnt) >= need) {
+                ready = true;
+                break;
+              }
+              if (it > 16) __nanosleep(32);
+              if ((it & 63) == 63 && (ld_acquire_gpu(p.sched + 1) != 0 || *abort_flag)) break;
+            }
+            if (!ready) {
+              if (ld_acquire_gpu(p.sched + 1) == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_DEP);
+              t = kTileDone;
+            }
+          }
+        }
+        ring[slot] = t;
+        st_cluster_u32(map_to_cta(ring_addr + 4u * slot, 1), t);
+        mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 0));
+        mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 1));
+        if (t == kTileDone) break;
+      }
+    }
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (uint32_t n = 0;; ++n) {
+        const uint32_t t = ring_get(n, true, ANC_DEV_TIMEOUT_TMA);
+        if (t == kTileDone) break;
+        const ChainTile ti = chain_decode(p, t);
+        fence_proxy_async_all();      // operands come from other CTAs' stores of the previous phase
+        const int cur = ti.k & 1;
+        const CUtensorMap *ma = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.b128);
+        const CUtensorMap *mb = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.xy64[cur]);
+        const int kblocks = (ti.mode == 0 ? p.N : p.M) / BK;
+        const int row0 = ti.e * p.M;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+            if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_TMA);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = base + s * kStageBytes2;
+          const uint32_t sb = sa + kABytes;
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (crank == 0) mbar_expect_tx(full_bar(s), 2u * kStageBytes2);
+          tma_load_2d_pair(sa, ma, kb * BK, row0 + ti.I * 256 + (int)crank * 128, lead_full);
+          if (ti.mode != 2) {
+            tma_load_2d_pair(sb, mb, kb * BK, row0 + ti.J * 256 + (int)crank * 128, lead_full);
+          } else {
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d_pair(sb + c * (64 * BK * 2), mb, ti.J * 256 + (int)crank * 128 + c * 64,
+                               row0 + kb * BK, lead_full);
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && crank == 0) {
+      uint32_t it = 0;
+      for (uint32_t n = 0;; ++n) {
+        const uint32_t t = ring_get(n, true, ANC_DEV_TIMEOUT_MMA);
+        if (t == kTileDone) break;
+        const ChainTile ti = chain_decode(p, t);
+        const bool nmajor_b = (ti.mode == 2);
+        const int kblocks = (ti.mode == 0 ? p.N : p.M) / BK;
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((nmajor_b ? 1u : 0u) << 16) |
+                               ((256u >> 3) << 17) | ((256u >> 4) << 24);
+        const uint32_t buf = n & 1;
+        const uint32_t aph = (n >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) {
+          if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 256u;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+            if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes2;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = nmajor_b ? make_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                         : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(s));
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, both CTAs)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const bool elected = (threadIdx.x == 64);
+    uint32_t d_loads = 0;            // tiles so far that fetched an axpy operand (parity of dfull_bar)
+    for (uint32_t n = 0;; ++n) {
+      const uint32_t t = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
+      __syncwarp();                 // every lane has read the slot before the warp releases it
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(sempty_bar((int)(n % kSchedSlots)), 0));
+      // also orders the elected thread's wait for the previous tile's stores before anybody
+      // writes the staging tile again
+      if (epi_bar_or(2, t == kTileDone)) break;
+      const ChainTile ti = chain_decode(p, t);
+      const int mode = ti.mode;
+      const int i = 2 * ti.I + (int)crank;
+      const int j = 2 * ti.J;
+      const int nblk = (mode == 2 || j + 1 <= i) ? 2 : 1;
+      const uint32_t buf = n & 1;
+      const uint32_t aph = (n >> 1) & 1;
+      const int grow0 = ti.e * p.M + i * BM;
+      const int cur = ti.k & 1;
+      // axpy operand D and output C of this phase
+      const CUtensorMap *md = mode == 1 ? &maps.a128 : &maps.xy128[cur];
+      const CUtensorMap *mc = mode == 0 ? &maps.a128 : (mode == 1 ? &maps.b128 : &maps.xy128[cur ^ 1]);
+      if (elected && mode != 0) {
+        // staging is free: the previous tile's stores were waited for before its completion was signalled
+        fence_proxy_async_all();
+        mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
+        for (int b = 0; b < 2 * nblk; ++b)
+          tma_load_2d(epi_base + b * kEpiBoxBytes, md, j * 128 + b * 64, grow0, dfull_bar);
+      }
+      bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
+      if (ok && mode != 0) ok = mbar_wait(dfull_bar, d_loads & 1, abort_flag);
+      ok = __all_sync(0xFFFFFFFFu, ok);     // the warp-wide TMEM loads below need a converged warp
+      if (mode != 0) ++d_loads;
+      if (!ok) {
+        if (lane == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
+      } else {
+        tc_fence_after();
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+        uint8_t *my_row = epi_gen + r * 128;
+        const bool scaled = p.mscale != nullptr && ti.k == 0 && mode != 1;
+        const float sc = scaled ? p.mscale[ti.e] : 1.f;
+        const float sc2 = __fmul_rn(sc, sc);
+        const float alpha = mode == 0 ? 0.f : (mode == 1 ? p.coef[3 * ti.k + 1] : p.coef[3 * ti.k]);
+        const float beta = mode == 1 ? p.coef[3 * ti.k + 2] : 1.f;
+        const float al = scaled ? __fmul_rn(alpha, sc) : alpha;
+        const float be = scaled ? __fmul_rn(beta, sc) : beta;
+        uint16_t *cmir = mode == 0 ? p.A : p.B;
+        for (int cc = 0; cc < 4 * nblk; ++cc) {
+          uint32_t v[32];
+          tc_ld32(taddr0 + cc * 32, v);
+          tc_wait_ld();
+          uint8_t *box_row = my_row + (cc >> 1) * kEpiBoxBytes;
+          const int c16 = (cc & 1) * 4;
+          uint32_t h[16];
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            uint4 *slot = reinterpret_cast<uint4 *>(box_row + (((c16 + k4) ^ (r & 7)) << 4));
+            float f[8];
+            if (mode == 0) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k4 * 8 + k])) : __uint_as_float(v[k4 * 8 + k]);
+            } else {
+              const uint4 d = *slot;
+              const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float dlo = __uint_as_float(dw[k] << 16);
+                const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
+                f[2 * k] = __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(al, dlo));
+                f[2 * k + 1] =
+                    __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) h[k4 * 4 + k] = pack_bf16(f[2 * k], f[2 * k + 1]);
+            *slot = make_uint4(h[k4 * 4], h[k4 * 4 + 1], h[k4 * 4 + 2], h[k4 * 4 + 3]);
+          }
+          const int hb = j + (cc >> 2);
+          if (mode != 2 && hb < i) {
+            const int col = j * 128 + cc * 32;
+            uint16_t *mcol = cmir + ((size_t)ti.e * p.M + (size_t)col) * p.M + (size_t)i * BM + r;
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        fence_async_smem();
+      }
+      // staging tile final; every mirrored store of this CTA issued
+      if (epi_bar_or(1, *abort_flag != 0)) break;
+      if (elected) {
+        for (int b = 0; b < 2 * nblk; ++b)
+          tma_store_2d(mc, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
+        bulk_commit();
+        bulk_wait0();               // stores complete (not only read out of staging)
+        fence_proxy_async_all();
+        __threadfence();            // with the barrier above: covers the other threads' mirrored stores too
+        red_release_gpu_add(p.sched + 2 + ti.e, 1u);
+      }
+    }
+    if (elected) bulk_wait0();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
   tc_fence_after();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -753,6 +1211,7 @@ struct GemmCache {
   std::map<uint64_t, TileTab> tabs;
   bool attr_set = false;
   bool attr2_set = false;
+  bool attr3_set = false;
 };
 std::map<anc_ctx *, GemmCache *> g_caches;
 std::mutex g_caches_mu;   // contexts of different threads may launch concurrently
@@ -907,6 +1366,85 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
   return ANC_OK;
 }
 
+bool anc_ns_chain_supported(const anc_ctx *ctx, int M, int N, int steps) {
+  const char *env = getenv("ANCORA_NS_CHAIN");
+  if (env && env[0] == '0') return false;       // fall back to one launch per phase
+  return steps >= 1 && steps <= kMaxChainSteps && M > 0 && M <= N && M % 256 == 0 && N % 256 == 0 &&
+         M / 256 <= 255 && N / 256 <= 255 && ctx->sm_count >= 2;
+}
+
+// The whole chain of `steps` iterations on E packed matrices in one persistent launch.
+// X holds the operand, Y is the second ping-pong buffer: the result is in X when steps is even,
+// in Y when it is odd.  sched: 2 + E words that are ZERO when the kernel starts (the Frobenius
+// finalize kernel clears them).  spin_limit = 0 selects the default bound of the waits.
+int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uint16_t *B, int E, int M, int N,
+                        int steps, const float *coeffs, const float *mscale, uint32_t *sched,
+                        uint32_t spin_limit, cudaStream_t st) {
+  ANC_REQUIRE(anc_ns_chain_supported(ctx, M, N, steps), "shape (%d,%d) x %d steps not supported by the chain kernel",
+              M, N, steps);
+  ANC_REQUIRE(E > 0 && (size_t)E * M < (1u << 31), "bad batch %d", E);
+  ANC_REQUIRE(sched, "scheduler words missing");
+  ChainMaps maps;
+  uint16_t *xy[2] = {X, Y};
+  int rc;
+  for (int b = 0; b < 2; ++b) {
+    if ((rc = make_map(&maps.xy128[b], xy[b], (uint64_t)E * M, (uint64_t)N, 128))) return rc;
+    if ((rc = make_map(&maps.xy64[b], xy[b], (uint64_t)E * M, (uint64_t)N, 64))) return rc;
+  }
+  if ((rc = make_map(&maps.a128, A, (uint64_t)E * M, (uint64_t)M, 128))) return rc;
+  if ((rc = make_map(&maps.b128, B, (uint64_t)E * M, (uint64_t)M, 128))) return rc;
+  TileTab ts, tf;
+  if ((rc = get_tile_tab(ctx, true, true, M / 128, M / 128, &ts))) return rc;
+  if ((rc = get_tile_tab(ctx, false, true, M / 128, N / 128, &tf))) return rc;
+  GemmCache *gc;
+  {
+    std::lock_guard<std::mutex> lock(g_caches_mu);
+    gc = g_caches[ctx];
+  }
+  if (!gc->attr3_set) {
+    ANC_CUDA(cudaFuncSetAttribute(ns_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes3));
+    gc->attr3_set = true;
+  }
+  ChainParams p;
+  memset(&p, 0, sizeof(p));
+  p.A = A;
+  p.B = B;
+  p.tab_sym = ts.d_tab;
+  p.tab_full = tf.d_tab;
+  p.mscale = mscale;
+  p.sched = sched;
+  p.status = ctx->d_status;
+  p.E = E;
+  p.M = M;
+  p.N = N;
+  p.steps = steps;
+  p.g = ts.count;
+  p.a = tf.count;
+  const uint64_t total = (uint64_t)steps * E * (2ull * ts.count + tf.count);
+  ANC_REQUIRE(total < 0xFFFFFF00ull, "too many tiles");
+  p.total_tiles = (uint32_t)total;
+  p.spin_limit = spin_limit ? spin_limit : kSpinLimit;
+  for (int i = 0; i < 3 * steps; ++i) p.coef[i] = coeffs[i];
+  uint64_t pairs = (uint64_t)(ctx->sm_count / 2);
+  if (total < pairs) pairs = total;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kChainThreads);
+  cfg.dynamicSmemBytes = kSmemBytes3;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  ANC_CUDA(cudaLaunchKernelEx(&cfg, ns_chain_kernel, maps, p));
+  return ANC_OK;
+}
+
 extern "C" int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q,
                                  uint16_t *C, int E, int M, int N, float alpha, float beta,
                                  void *stream) {
@@ -914,4 +1452,33 @@ extern "C" int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, cons
   anc_device_guard guard(ctx->device);
   return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, nullptr,
                             anc_pick_stream(ctx, stream));
+}
+
+// Launches the chain kernel on a 256x256 matrix with the tile counter preset past the first
+// phase, so the first claimed tile depends on a phase that never runs: its bounded wait must
+// run out, set ANC_DEV_TIMEOUT_DEP in the context's status word and let every role drain.
+extern "C" int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  ANC_REQUIRE(spin_limit > 0 && spin_limit <= (1u << 20), "spin_limit must be in [1, 2^20]");
+  anc_device_guard guard(ctx->device);
+  const int M = 256;
+  const size_t bytes = (size_t)M * M * 2;
+  char *buf = nullptr;
+  ANC_CUDA(cudaMalloc((void **)&buf, 4 * bytes + 256));
+  cudaError_t e = cudaMemsetAsync(buf, 0, 4 * bytes + 256, ctx->stream);
+  uint32_t *sched = (uint32_t *)(buf + 4 * bytes);
+  const uint32_t first_tile = 1;     // tile 0 is the only gram tile; tile 1 (poly) waits for it
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(sched, &first_tile, sizeof(first_tile), cudaMemcpyHostToDevice, ctx->stream);
+  int rc = e == cudaSuccess ? ANC_OK : anc_cuda_fail(e, "selftest set-up");
+  const float coef[3] = {1.f, 1.f, 1.f};
+  if (!rc)
+    rc = anc_launch_ns_chain(ctx, (uint16_t *)buf, (uint16_t *)(buf + bytes), (uint16_t *)(buf + 2 * bytes),
+                             (uint16_t *)(buf + 3 * bytes), 1, M, M, 1, coef, nullptr, sched, spin_limit,
+                             ctx->stream);
+  e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(buf);
+  if (rc) return rc;
+  if (e != cudaSuccess) return anc_cuda_fail(e, "selftest sync");
+  return ANC_OK;
 }

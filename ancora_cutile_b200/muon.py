@@ -77,11 +77,11 @@ class MuonPlan:
 
     def last_timing(self):
         ms = (C.c_float * 4)()
-        fl = C.c_double()
+        fl = (C.c_double * 2)()
         nl = C.c_int()
-        L.check(L.lib().anc_muon_plan_last_timing(self.handle, ms, C.byref(fl), C.byref(nl)))
+        L.check(L.lib().anc_muon_plan_last_timing(self.handle, ms, fl, C.byref(nl)))
         return dict(momentum_ms=ms[0], normalize_ms=ms[1], ns_ms=ms[2], update_ms=ms[3],
-                    ns_flops=fl.value, ns_launches=nl.value)
+                    ns_flops=fl[0], ns_flops_executed=fl[1], ns_launches=nl.value)
 
     def scratch_bytes(self):
         b = C.c_uint64()

@@ -226,11 +226,19 @@ ANC_API int anc_muon_step_range(anc_muon_plan *plan, int group, int first, int c
 /* Per-phase device time accumulated over every anc_muon_step since the previous call
  * (timing enabled with anc_muon_plan_set_timing(plan, 1); CUDA events on the step's
  * stream, no synchronisation inside the step): ms spent in momentum, normalise,
- * Newton-Schulz GEMMs and update; the algorithmic FLOPs and the launch count of those
- * GEMMs.  The call waits for the recorded events, then resets the accumulators. */
+ * Newton-Schulz GEMMs and update; ns_flops[0] the algorithmic (dense) FLOPs of those GEMMs,
+ * ns_flops[1] the FLOPs the tensor cores executed (the symmetric phases compute only the
+ * tiles on or below the diagonal); the launch count of the GEMM kernels.  The call waits
+ * for the recorded events, then resets the accumulators. */
 ANC_API int anc_muon_plan_set_timing(anc_muon_plan *plan, int on);
-ANC_API int anc_muon_plan_last_timing(anc_muon_plan *plan, float ms[4], double *ns_flops,
+ANC_API int anc_muon_plan_last_timing(anc_muon_plan *plan, float ms[4], double ns_flops[2],
                                       int *ns_launches);
+/* Self-test of the bounded waits (no counterpart in the reference): runs the chain kernel on
+ * a zeroed 256x256 matrix with the first phase skipped, so that a tile waits for a
+ * dependency nobody completes.  The wait gives up after `spin_limit` polls (<= 2^20), the
+ * kernel drains and returns, and status bit 0x10 is set in the context's status word; the
+ * context stays usable.  Synchronises the context's stream. */
+ANC_API int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit);
 ANC_API int anc_muon_plan_scratch_bytes(anc_muon_plan *plan, uint64_t *bytes);
 ANC_API int anc_muon_plan_destroy(anc_muon_plan *plan);
 

@@ -17,14 +17,22 @@ before importing.  Only host (numpy) code of the reference is executed:
 * ancora.kernels.quant._e4m3_table/f32_to_e4m3/
   dequantize_rowblock (host helpers)          -> e4m3.npz
 
-The reference's AdamW runs only on a GPU (cuda.tile kernel); it has no host
-function to call, so AdamW has no file here: its oracle is pinned by the formula
-the reference's own test states (tests/optim/test_adamw.py:37-41) at that test's
-tolerance, in tests/test_oracle_golden.py.
+* the four arithmetic statements of the
+  ancora.optim.adamw._adamw kernel body,
+  read from the source file and evaluated on
+  float32 numpy arrays                        -> adamw.npz
+
+The reference's AdamW runs only on a GPU (cuda.tile kernel) and has no host function to
+call.  Its arithmetic is four statements of plain operator syntax (adamw.py:34-37), so the
+generator reads those statements from the checkout and executes their text with numpy
+float32 arrays for the tiles, numpy float32 scalars for the runtime scalars and
+``ct.sqrt = numpy.sqrt``: operator precedence and association are then the reference's own
+text, not a reading of it.  A change of operation order in the reference changes adamw.npz.
 """
 import importlib.util
 import json
 import os
+import re
 import sys
 import types
 
@@ -122,6 +130,33 @@ def main(ref_root):
     sc = rq.integers(100, 140, (64, 2)).astype(np.uint8)
     np.savez_compressed(os.path.join(HERE, "e4m3.npz"), table=_e4m3_table(), x=xq, bytes=f32_to_e4m3(xq),
                         fp8=fp8, scale=sc, dequant=dequantize_rowblock(fp8, sc).astype(np.float32))
+    # 7. AdamW: the kernel body's arithmetic statements, executed as written
+    text = open(os.path.join(ref_root, "ancora", "optim", "adamw.py")).read().splitlines()
+    body = [l.strip() for l in text if re.match(r"\s+(mn|vn|upd|pn)\s*=", l)]
+    assert [l.split("=")[0].strip() for l in body] == ["mn", "vn", "upd", "pn"], body
+    ra = np.random.default_rng(0)
+    n = 1 << 14
+    f = np.float32
+    p = (ra.standard_normal(n) * 0.02).astype(f)
+    m = (ra.standard_normal(n) * 1e-4).astype(f)
+    v = np.abs(ra.standard_normal(n) * 1e-6).astype(f)
+    g = _bits_f32(_bf16_bits((ra.standard_normal(n) * 1e-3).astype(f))).astype(f)      # bf16-valued gradient
+    p[:8] = [0.0, -0.0, 1.0, -1.0, 3e38, -3e38, 1e-30, 65504.0]
+    v[:4] = [0.0, 1e-38, 1e10, 1e-12]
+    g[4:8] = [0.0, 1.0, -1.0, 1e-20]
+    lr, b1, b2, eps, wd, t = 3e-4, 0.9, 0.95, 1e-8, 0.1, 10
+    env = dict(ct=types.SimpleNamespace(sqrt=np.sqrt), g=g, tm=m, tv=v, tp=p,
+               beta1=f(b1), beta2=f(b2), eps=f(eps), lr=f(lr), wd=f(wd),
+               ibc1=f(1.0 / (1.0 - b1 ** t)), ibc2=f(1.0 / (1.0 - b2 ** t)))   # scalars as adamw.py:90-97 passes them
+    with np.errstate(all="ignore"):
+        for stmt in body:
+            exec(stmt, env)
+    for k in ("mn", "vn", "pn"):
+        assert env[k].dtype == np.float32, (k, env[k].dtype)
+    np.savez_compressed(os.path.join(HERE, "adamw.npz"), p=p, m=m, v=v, g=g,
+                        hyper=np.array([lr, b1, b2, eps, wd, t], np.float64),
+                        mn=env["mn"], vn=env["vn"], pn=env["pn"], p16=_bf16_bits(env["pn"]),
+                        statements=np.array(body))
     print("wrote fixtures to", HERE)
 
 

@@ -123,6 +123,55 @@ def test_odd_step_count_lands_in_x(ctx):
         assert c > 0.999 and r < 0.02, (steps, c, r)
 
 
+def test_group_1024x1024_pe5_and_batch_of_seven(ctx):
+    """The (1024,1024) shape group (k/v projections): Polar-Express x5 against the fp32 chain at
+    the reference's bar (tests/kernels/_probe_polar_express_device.py:72-78), and a batch of 7
+    (one rank's share at 8 GPUs) bitwise equal to each matrix run alone."""
+    rng = np.random.default_rng(7)
+    E, M, N = 7, 1024, 1024
+    Ws = [f32_to_bf16_bits((rng.standard_normal((M, N)) * 1e-3).astype(np.float32)) for _ in range(E)]
+    out = dev_ns(ctx, np.concatenate(Ws, 0), E, M, N, 5, muon_ns.PE_SCHEDULE)
+    for e in (0, 6):
+        c, r = cos_rel(bits_to_f32(out[e * M:(e + 1) * M]), muon_ref.ns_fp32(bits_to_f32(Ws[e]), 5, muon_ref.PE_SCHEDULE))
+        assert c > 0.999 and r < 0.02, (e, c, r)
+    for e in (0, 3, 6):
+        assert np.array_equal(dev_ns(ctx, Ws[e], 1, M, N, 5, muon_ns.PE_SCHEDULE), out[e * M:(e + 1) * M]), e
+
+
+@pytest.mark.parametrize("E,M,N,steps", [(1, 256, 256, 1), (3, 256, 512, 2), (5, 512, 1024, 5), (7, 1024, 1024, 5),
+                                         (16, 768, 1024, 5), (2, 1024, 3072, 4), (11, 1024, 3072, 5),
+                                         (40, 256, 256, 3)])
+def test_single_launch_chain_equals_one_launch_per_phase(ctx, monkeypatch, E, M, N, steps):
+    """The persistent chain kernel (dynamic tile queue over all phases, per-matrix dependency
+    counters) must give the bits of the phase-by-phase launches: same tiles, same K order."""
+    rng = np.random.default_rng(E * 1000 + M + N + steps)
+    Xb = f32_to_bf16_bits((rng.standard_normal((E * M, N)) * 1e-3).astype(np.float32))
+    monkeypatch.setenv("ANCORA_NS_CHAIN", "0")
+    per_phase = dev_ns(ctx, Xb, E, M, N, steps, muon_ns.PE_SCHEDULE)
+    monkeypatch.delenv("ANCORA_NS_CHAIN")
+    chain = dev_ns(ctx, Xb, E, M, N, steps, muon_ns.PE_SCHEDULE)
+    assert np.array_equal(chain, per_phase)
+    for _ in range(3):                              # dynamic scheduling must not show in the bits
+        assert np.array_equal(dev_ns(ctx, Xb, E, M, N, steps, muon_ns.PE_SCHEDULE), chain)
+
+
+def test_dependency_wait_runs_out_and_context_survives(ctx):
+    """A tile whose dependency nobody completes: the bounded wait gives up, status bit 0x10 is
+    set, the kernel drains and returns, and the context keeps working (no trap, no hang)."""
+    import ctypes as C
+    from ancora_cutile_b200 import _lib as L
+    ctx.sync()
+    assert ctx.status() == 0
+    L.check(L.lib().anc_ns_chain_wait_selftest(ctx.handle, C.c_uint32(2000)))
+    assert ctx.status() == 0x10
+    assert ctx.status() == 0                                       # reading clears it
+    rng = np.random.default_rng(9)
+    Xb = f32_to_bf16_bits(rng.standard_normal((256, 256)).astype(np.float32))
+    got = bits_to_f32(dev_ns(ctx, Xb, 1, 256, 256, 5, muon_ns.PE_SCHEDULE))     # ordinary work still runs
+    c, r = cos_rel(got, muon_ref.ns_fp32(bits_to_f32(Xb), 5, muon_ref.PE_SCHEDULE))
+    assert c > 0.999 and r < 0.02
+
+
 def test_shape_errors(ctx):
     d = anc.DBuf.zeros((128, 128), np.uint16, ctx)
     r = anc.DBuf.zeros((1,), np.float32, ctx)

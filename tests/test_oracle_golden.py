@@ -119,6 +119,22 @@ def test_adamw_oracle_vs_reference_test_formula():
             assert np.array_equal(p16, bf16.rne_bits(p))
 
 
+def test_adamw_oracle_equals_the_reference_kernel_statements_bit_for_bit():
+    """adamw.npz holds the outputs of the reference kernel's own four arithmetic statements
+    (ancora/optim/adamw.py:34-37), read from its source and executed on float32 numpy arrays by
+    tests/golden/make_golden.py.  The oracle must reproduce them exactly, so its operation order
+    is pinned to the reference's text."""
+    z = np.load(os.path.join(G, "adamw.npz"))
+    assert [s.split("=")[0].strip() for s in z["statements"]] == ["mn", "vn", "upd", "pn"]
+    lr, b1, b2, eps, wd, t = z["hyper"]
+    s = adamw_ref.adamw_scalars(lr, b1, b2, eps, int(t))
+    with np.errstate(all="ignore"):
+        pn, mn, vn, p16 = adamw_ref.adamw_step(z["p"], z["m"], z["v"], z["g"], s, wd, "rne")
+    for name, got in (("mn", mn), ("vn", vn), ("pn", pn)):
+        assert np.array_equal(got.view(np.uint32), z[name].view(np.uint32)), name
+    assert np.array_equal(p16, z["p16"])
+
+
 def test_adamw_scalars_definition():
     s = adamw_ref.adamw_scalars(3e-4, 0.9, 0.95, 1e-8, 10)
     assert s.omb1 == np.float32(1.0) - np.float32(0.9)          # float32 subtraction, adamw.py:34
