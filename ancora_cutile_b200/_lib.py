@@ -62,6 +62,7 @@ SIGNATURES = {
     "anc_d2h": (_i, [_vp, _vp, _vp, _sz, _vp, _i]),
     "anc_d2d": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "anc_host_alloc": (_i, [_sz, _pp]),
+    "anc_host_alloc_near": (_i, [_i, _sz, _pp]),
     "anc_host_free": (_i, [_vp]),
     "anc_event_create": (_i, [_pp]),
     "anc_event_record": (_i, [_vp, _vp]),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "anc_adamw_plan_total": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "anc_adamw_step": (_i, [_vp, C.POINTER(AdamWScalars), _i, _u64, _u64, _vp]),
     "anc_adamw_plan_set_schedule": (_i, [_vp, C.POINTER(AdamWScalars), _i, _u64]),
+    "anc_adamw_plan_set_counter": (_i, [_vp, _u64, _vp]),
     "anc_adamw_step_scheduled": (_i, [_vp, _i, _u64, _i, _vp]),
     "anc_adamw_plan_destroy": (_i, [_vp]),
     "anc_muon_plan_create": (_i, [_vp, C.POINTER(MuonWeight), _i, _i, _i, _i, _pp]),
@@ -97,6 +99,7 @@ SIGNATURES = {
     "anc_ns_gemm_phase": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "anc_muon_momentum": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _i, _vp]),
     "anc_muon_update": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "anc_ns_batched_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_f), _f, _i, _vp]),
     "anc_ns_chain_wait_selftest": (_i, [_vp, C.c_uint32]),
     "anc_fro_normalize": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "anc_fro_normalize_static": (_i, [_i, _vp, _vp, _i, _i, _i, _f, _vp]),

@@ -92,6 +92,10 @@ class ResidentAdamW:
         tab = (L.AdamWScalars * n)(*[step_scalars(lr, b1, b2, eps, first_step + k) for k in range(n)])
         L.check(L.lib().anc_adamw_plan_set_schedule(self.handle, tab, n, int(first_step)))
 
+    def set_counter(self, step, si=None):
+        """Points the device step counter at ``step`` (must lie inside the uploaded schedule)."""
+        L.check(L.lib().anc_adamw_plan_set_counter(self.handle, int(step), C.c_void_p(si or None)))
+
     def step_scheduled(self, si=None, advance=True):
         """The step whose number is in the device counter; capturable in a CUDA graph."""
         L.check(L.lib().anc_adamw_step_scheduled(self.handle, _ROUND[self.rounding], self.seed,

@@ -179,12 +179,16 @@ class DBuf:
 class PinnedArray:
     """Page-locked host memory viewed as a numpy array (staging for host<->device)."""
 
-    def __init__(self, shape, dtype):
+    def __init__(self, shape, dtype, device=None):
+        """device: place the pages on the NUMA node next to that GPU."""
         self.shape = tuple(shape) if not isinstance(shape, int) else (shape,)
         self.dtype = np.dtype(dtype)
         self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
         p = C.c_void_p()
-        L.check(L.lib().anc_host_alloc(max(self.nbytes, 1), C.byref(p)))
+        if device is None:
+            L.check(L.lib().anc_host_alloc(max(self.nbytes, 1), C.byref(p)))
+        else:
+            L.check(L.lib().anc_host_alloc_near(int(device), max(self.nbytes, 1), C.byref(p)))
         self.ptr = p.value
         buf = (C.c_char * max(self.nbytes, 1)).from_address(self.ptr)
         self.array = np.frombuffer(buf, dtype=self.dtype, count=int(np.prod(self.shape, dtype=np.int64))).reshape(self.shape)

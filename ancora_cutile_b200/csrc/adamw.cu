@@ -346,6 +346,20 @@ int anc_adamw_plan_set_schedule(anc_adamw_plan *plan, const anc_adamw_scalars *t
   return ANC_OK;
 }
 
+int anc_adamw_plan_set_counter(anc_adamw_plan *plan, uint64_t step, void *stream) {
+  ANC_REQUIRE(plan, "plan is NULL");
+  ANC_REQUIRE(plan->d_sched && plan->d_counter, "no schedule: call anc_adamw_plan_set_schedule first");
+  ANC_REQUIRE(step >= plan->sched_first && step < plan->sched_first + plan->sched_len,
+              "step %llu is outside the uploaded schedule [%llu, %llu)", (unsigned long long)step,
+              (unsigned long long)plan->sched_first, (unsigned long long)(plan->sched_first + plan->sched_len));
+  anc_device_guard guard(plan->ctx->device);
+  cudaStream_t st = anc_pick_stream(plan->ctx, stream);
+  ANC_CUDA(cudaStreamSynchronize(st));      // no launch that reads the counter is still in flight
+  unsigned long long t0 = step;
+  ANC_CUDA(cudaMemcpy(plan->d_counter, &t0, sizeof(t0), cudaMemcpyHostToDevice));
+  return ANC_OK;
+}
+
 int anc_adamw_step_scheduled(anc_adamw_plan *plan, int rounding, uint64_t seed, int advance,
                              void *stream) {
   ANC_REQUIRE(plan, "plan is NULL");

@@ -386,6 +386,12 @@ int anc_muon_plan_destroy(anc_muon_plan *pl) {
 
 int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y, float *recip,
                    int E, int M, int N, int steps, const float *coeffs, float eps, void *stream) {
+  return anc_ns_batched_ex(ctx, X, A, B, Y, recip, E, M, N, steps, coeffs, eps, 1, stream);
+}
+
+int anc_ns_batched_ex(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y, float *recip,
+                      int E, int M, int N, int steps, const float *coeffs, float eps, int single_launch,
+                      void *stream) {
   ANC_REQUIRE(ctx && X && A && B && Y && recip && (coeffs || steps == 0), "NULL argument");
   ANC_REQUIRE(M <= N, "Newton-Schulz needs M <= N (got %d x %d); transpose tall weights first", M, N);
   ANC_REQUIRE(M % 128 == 0 && N % 128 == 0, "NS shape (%d,%d) must be multiples of 128", M, N);
@@ -412,7 +418,7 @@ int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t
   rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, eps, sched, st);
   if (rc) return rc;
   uint16_t *x = X, *y = Y;
-  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, sched, st);
+  rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, single_launch ? sched : nullptr, st);
   if (rc) return rc;
   if (x != X)   // odd number of steps: result sits in Y, copy it home (muon_ns.py:274-276)
     ANC_CUDA(cudaMemcpyAsync(X, x, (size_t)E * M * N * 2, cudaMemcpyDeviceToDevice, st));

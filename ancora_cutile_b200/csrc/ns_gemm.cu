@@ -418,6 +418,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar_cluster_addr)
       : "memory");
 }
+// Asks L2 to fetch a box ahead of the load that will bring it into shared memory: the smem ring
+// only covers an L2 hit's latency, so the DRAM latency is taken here, several K blocks earlier.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
   asm volatile(
@@ -730,14 +736,17 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // The tile -> output mapping and each tile's K order are those of the per-phase kernel, so
 // the results are bitwise the same.
 //
-// Roles (224 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-5
+// Roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-5
 // epilogue, warp 6 scheduler (leader CTA): it claims a tile, waits for the tile's
-// dependencies and publishes it to both CTAs through a small ring in shared memory.
+// dependencies, decodes it and publishes it to both CTAs through a small ring in shared
+// memory; warp 7 stores the finished staging tile (TMA), waits for the store to complete and
+// then raises the matrix's completion counter, so that latency never sits in the epilogue.
 // Every wait is bounded; a wait that runs out raises the launch-wide abort word, and all
 // roles drain and return.
 // ====================================================================================
-constexpr int kChainThreads = 224;
+constexpr int kChainThreads = 256;
 constexpr int kSchedSlots = 3;
+constexpr int kPrefetchAhead = 8;      // K blocks the L2 prefetch runs ahead of the shared-memory load (default)
 constexpr int kMaxChainSteps = 16;
 constexpr uint32_t kTileDone = 0xFFFFFFFFu;
 constexpr int kSmemBytes3 = kStages2 * kStageBytes2 + kEpiBytes + 1024 + 512;
@@ -758,16 +767,20 @@ struct ChainParams {
   int g, a;                            // tiles per matrix in a symmetric phase / in the apply phase
   uint32_t total_tiles;
   uint32_t spin_limit;
+  int prefetch;                        // K blocks of L2 prefetch ahead of the loads (0: none)
   float coef[3 * kMaxChainSteps];
 };
 
+// A published tile: iteration k, phase (0 gram, 1 poly, 2 apply), matrix e, pair-tile (I, J).
 struct ChainTile {
+  uint32_t t;
   int k, mode, e, I, J;
 };
 
 __device__ __forceinline__ ChainTile chain_decode(const ChainParams &p, uint32_t t) {
   const uint32_t per_it = (uint32_t)p.E * (2u * (uint32_t)p.g + (uint32_t)p.a);
   ChainTile ti;
+  ti.t = t;
   ti.k = (int)(t / per_it);
   uint32_t r = t - (uint32_t)ti.k * per_it;
   const uint32_t eg = (uint32_t)p.E * (uint32_t)p.g;
@@ -786,6 +799,21 @@ __device__ __forceinline__ ChainTile chain_decode(const ChainParams &p, uint32_t
   const uint32_t tt = (ti.mode == 2 ? p.tab_full : p.tab_sym)[l];
   ti.I = (int)(tt & 0xFF);
   ti.J = (int)((tt >> 8) & 0xFF);
+  return ti;
+}
+// Ring slot: {t, k | mode << 8 | I << 16 | J << 24, e, 0}
+__device__ __forceinline__ uint4 chain_pack(const ChainTile &ti) {
+  return make_uint4(ti.t, (uint32_t)ti.k | ((uint32_t)ti.mode << 8) | ((uint32_t)ti.I << 16) | ((uint32_t)ti.J << 24),
+                    (uint32_t)ti.e, 0u);
+}
+__device__ __forceinline__ ChainTile chain_unpack(const uint4 w) {
+  ChainTile ti;
+  ti.t = w.x;
+  ti.k = (int)(w.y & 0xFF);
+  ti.mode = (int)((w.y >> 8) & 0xFF);
+  ti.I = (int)((w.y >> 16) & 0xFF);
+  ti.J = (int)((w.y >> 24) & 0xFF);
+  ti.e = (int)w.z;
   return ti;
 }
 
@@ -815,6 +843,19 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.volatile.shared::cta.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *ptr) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
@@ -835,26 +876,27 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
   uint8_t *gen_base = smem_raw + (base - raw);
   const uint32_t epi_base = base + kStages2 * kStageBytes2;
   uint8_t *epi_gen = gen_base + kStages2 * kStageBytes2;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_gen + kEpiBytes);
-  const uint32_t bar0 = epi_base + kEpiBytes;
+  // after the staging tile: the ring (16-byte slots), then the barriers, then two words
+  const uint32_t ring_addr = epi_base + kEpiBytes;
+  const uint32_t bar0 = ring_addr + 16u * kSchedSlots;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_gen + kEpiBytes + 16 * kSchedSlots);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + 2 + b); };
-  const uint32_t dfull_bar = bar0 + 8u * (2 * kStages2 + 4);
-  auto sfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 5 + s); };                 // tile published
-  auto sempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 5 + kSchedSlots + s); };  // slot read by all
-  constexpr int kNumBars = 2 * kStages2 + 5 + 2 * kSchedSlots;
+  const uint32_t dfull_bar = bar0 + 8u * (2 * kStages2 + 4);      // axpy operand landed in staging
+  const uint32_t stg_full_bar = bar0 + 8u * (2 * kStages2 + 5);   // staging tile final, ready to store
+  const uint32_t stg_free_bar = bar0 + 8u * (2 * kStages2 + 6);   // the store has read staging out
+  auto sfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 7 + s); };                 // tile published
+  auto sempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 7 + kSchedSlots + s); };  // slot read by all
+  constexpr int kNumBars = 2 * kStages2 + 7 + 2 * kSchedSlots;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  volatile uint32_t *ring = reinterpret_cast<volatile uint32_t *>(tmem_slot + 2);
-  const uint32_t ring_addr = bar0 + 8u * kNumBars + 8u;
   const uint32_t abort_addr = bar0 + 8u * kNumBars + 4u;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();
-  const uint32_t limit = p.spin_limit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages2; ++s) {
@@ -866,10 +908,13 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       mbar_init(tempty_bar(b), 8);
     }
     mbar_init(dfull_bar, 1);
+    mbar_init(stg_full_bar, 4);      // one arrival per epilogue warp
+    mbar_init(stg_free_bar, 1);
     for (int s = 0; s < kSchedSlots; ++s) {
       mbar_init(sfull_bar(s), 1);
-      // readers of a slot: leader's producer, MMA issuer and 4 epilogue warps; peer's producer and 4 epilogue warps
-      mbar_init(sempty_bar(s), 11);
+      // readers of a slot: the leader's producer, MMA issuer, 4 epilogue warps and store thread (7),
+      // the peer's producer, 4 epilogue warps and store thread (6); the leader's copy is in use
+      mbar_init(sempty_bar(s), 13);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -897,35 +942,40 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     st_cluster_u32(map_to_cta(abort_addr, crank ^ 1u), 1u);
     atomicExch(&p.sched[1], 1u);
   };
-  // Next tile of this role (n-th tile of the pair), or kTileDone.  The scheduler publishes a
-  // tile only after its dependency wait (bounded by p.spin_limit), so this wait uses the long
-  // fixed bound: it must outlast the scheduler's.
-  auto ring_get = [&](uint32_t n, bool arrive, uint32_t bit) -> uint32_t {
+  // n-th tile of this pair for the calling role; tile.t == kTileDone ends the role.  The
+  // scheduler publishes a tile only after its dependency wait (bounded by p.spin_limit), so
+  // this wait uses the long fixed bound: it must outlast the scheduler's.
+  auto ring_get = [&](uint32_t n, bool arrive, uint32_t bit) -> ChainTile {
     const int slot = (int)(n % kSchedSlots);
     if (!mbar_wait_cluster(sfull_bar(slot), (n / kSchedSlots) & 1u, abort_flag, kSpinLimit)) {
       if (!*abort_flag) raise_abort(bit);
-      return kTileDone;
+      ChainTile none;
+      none.t = kTileDone;
+      none.k = none.mode = none.e = none.I = none.J = 0;
+      return none;
     }
-    const uint32_t t = ring[slot];
+    const ChainTile ti = chain_unpack(ld_shared_v4(ring_addr + 16u * slot));
     if (arrive) mbar_arrive_cluster(map_to_cta(sempty_bar(slot), 0));
-    return t;
+    return ti;
   };
 
   if (warp == 6) {
     // ------------------------------------------------------------ scheduler (leader only)
     if (lane == 0 && crank == 0) {
+      const uint32_t limit = p.spin_limit;
       const uint32_t per_e_it = 2u * (2u * (uint32_t)p.g + (uint32_t)p.a);   // half-tiles per matrix and iteration
       for (uint32_t n = 0;; ++n) {
         const int slot = (int)(n % kSchedSlots);
-        uint32_t t = kTileDone;
+        ChainTile ti;
+        ti.t = kTileDone;
+        ti.k = ti.mode = ti.e = ti.I = ti.J = 0;
         if (mbar_wait_cluster(sempty_bar(slot), ((n / kSchedSlots) & 1u) ^ 1u, abort_flag, kSpinLimit)) {
-          t = atomicAdd(&p.sched[0], 1u);
-          if (t >= p.total_tiles) t = kTileDone;
+          const uint32_t t = atomicAdd(&p.sched[0], 1u);
+          if (t < p.total_tiles) ti = chain_decode(p, t);
         } else if (!*abort_flag) {
           raise_abort(ANC_DEV_TIMEOUT_DEP);
         }
-        if (t != kTileDone) {
-          const ChainTile ti = chain_decode(p, t);
+        if (ti.t != kTileDone) {
           const uint32_t need = (uint32_t)ti.k * per_e_it +
                                 (ti.mode == 1 ? 2u * (uint32_t)p.g : (ti.mode == 2 ? 4u * (uint32_t)p.g : 0u));
           if (need) {
@@ -941,15 +991,16 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
             }
             if (!ready) {
               if (ld_acquire_gpu(p.sched + 1) == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_DEP);
-              t = kTileDone;
+              ti.t = kTileDone;
             }
           }
         }
-        ring[slot] = t;
-        st_cluster_u32(map_to_cta(ring_addr + 4u * slot, 1), t);
+        const uint4 w = chain_pack(ti);
+        st_cluster_v4(map_to_cta(ring_addr + 16u * slot, 0), w);
+        st_cluster_v4(map_to_cta(ring_addr + 16u * slot, 1), w);
         mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 0));
         mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 1));
-        if (t == kTileDone) break;
+        if (ti.t == kTileDone) break;
       }
     }
   } else if (warp == 0) {
@@ -957,19 +1008,33 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       for (uint32_t n = 0;; ++n) {
-        const uint32_t t = ring_get(n, true, ANC_DEV_TIMEOUT_TMA);
-        if (t == kTileDone) break;
-        const ChainTile ti = chain_decode(p, t);
+        const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_TMA);
+        if (ti.t == kTileDone) break;
         fence_proxy_async_all();      // operands come from other CTAs' stores of the previous phase
         const int cur = ti.k & 1;
         const CUtensorMap *ma = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.b128);
         const CUtensorMap *mb = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.xy64[cur]);
         const int kblocks = (ti.mode == 0 ? p.N : p.M) / BK;
         const int row0 = ti.e * p.M;
+        const int arow = row0 + ti.I * 256 + (int)crank * 128;
+        const int brow = row0 + ti.J * 256 + (int)crank * 128;   // K-major B operand
+        const int bcol = ti.J * 256 + (int)crank * 128;          // N-major B operand (apply)
+        auto prefetch = [&](int kb) {
+          tma_prefetch_2d(ma, kb * BK, arow);
+          if (ti.mode != 2) {
+            tma_prefetch_2d(mb, kb * BK, brow);
+          } else {
+            tma_prefetch_2d(mb, bcol, row0 + kb * BK);
+            tma_prefetch_2d(mb, bcol + 64, row0 + kb * BK);
+          }
+        };
+        const int ahead = p.prefetch;
+        for (int kb = 0; kb < ahead && kb < kblocks; ++kb) prefetch(kb);
         bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kStages2;
           const uint32_t ph = (it / kStages2) & 1;
+          if (ahead > 0 && kb + ahead < kblocks) prefetch(kb + ahead);
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
             if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_TMA);
             ok = false;
@@ -979,13 +1044,12 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
           const uint32_t sb = sa + kABytes;
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
           if (crank == 0) mbar_expect_tx(full_bar(s), 2u * kStageBytes2);
-          tma_load_2d_pair(sa, ma, kb * BK, row0 + ti.I * 256 + (int)crank * 128, lead_full);
+          tma_load_2d_pair(sa, ma, kb * BK, arow, lead_full);
           if (ti.mode != 2) {
-            tma_load_2d_pair(sb, mb, kb * BK, row0 + ti.J * 256 + (int)crank * 128, lead_full);
+            tma_load_2d_pair(sb, mb, kb * BK, brow, lead_full);
           } else {
             for (int c = 0; c < 2; ++c)
-              tma_load_2d_pair(sb + c * (64 * BK * 2), mb, ti.J * 256 + (int)crank * 128 + c * 64,
-                               row0 + kb * BK, lead_full);
+              tma_load_2d_pair(sb + c * (64 * BK * 2), mb, bcol + c * 64, row0 + kb * BK, lead_full);
           }
         }
         if (!ok) break;
@@ -996,9 +1060,8 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     if (lane == 0 && crank == 0) {
       uint32_t it = 0;
       for (uint32_t n = 0;; ++n) {
-        const uint32_t t = ring_get(n, true, ANC_DEV_TIMEOUT_MMA);
-        if (t == kTileDone) break;
-        const ChainTile ti = chain_decode(p, t);
+        const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_MMA);
+        if (ti.t == kTileDone) break;
         const bool nmajor_b = (ti.mode == 2);
         const int kblocks = (ti.mode == 0 ? p.N : p.M) / BK;
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((nmajor_b ? 1u : 0u) << 16) |
@@ -1036,6 +1099,34 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         tc_commit_pair(tfull_bar(buf));
       }
     }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------ store + completion signal (both CTAs)
+    if (lane == 0) {
+      for (uint32_t n = 0;; ++n) {
+        const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_EPI);
+        if (ti.t == kTileDone) break;
+        const int i = 2 * ti.I + (int)crank;
+        const int j = 2 * ti.J;
+        const int nblk = (ti.mode == 2 || j + 1 <= i) ? 2 : 1;
+        const int grow0 = ti.e * p.M + i * BM;
+        const int cur = ti.k & 1;
+        const CUtensorMap *mc = ti.mode == 0 ? &maps.a128 : (ti.mode == 1 ? &maps.b128 : &maps.xy128[cur ^ 1]);
+        if (!mbar_wait(stg_full_bar, n & 1u, abort_flag)) {
+          if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
+          break;
+        }
+        for (int b = 0; b < 2 * nblk; ++b)
+          tma_store_2d(mc, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
+        bulk_commit();
+        bulk_wait_read0();            // staging read out: the epilogue may write it again
+        mbar_arrive(stg_free_bar);
+        bulk_wait0();                 // stores complete
+        fence_proxy_async_all();
+        __threadfence();              // also covers the epilogue threads' mirrored stores (ordered by stg_full)
+        red_release_gpu_add(p.sched + 2 + ti.e, 1u);
+      }
+      bulk_wait0();
+    }
   } else {
     // ------------------------------------------------------------ epilogue (4 warps, both CTAs)
     const int q = warp & 3;
@@ -1043,13 +1134,10 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     const bool elected = (threadIdx.x == 64);
     uint32_t d_loads = 0;            // tiles so far that fetched an axpy operand (parity of dfull_bar)
     for (uint32_t n = 0;; ++n) {
-      const uint32_t t = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
+      const ChainTile ti = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
       __syncwarp();                 // every lane has read the slot before the warp releases it
       if (lane == 0) mbar_arrive_cluster(map_to_cta(sempty_bar((int)(n % kSchedSlots)), 0));
-      // also orders the elected thread's wait for the previous tile's stores before anybody
-      // writes the staging tile again
-      if (epi_bar_or(2, t == kTileDone)) break;
-      const ChainTile ti = chain_decode(p, t);
+      if (epi_bar_or(2, ti.t == kTileDone)) break;      // uniform over the 128 threads
       const int mode = ti.mode;
       const int i = 2 * ti.I + (int)crank;
       const int j = 2 * ti.J;
@@ -1058,20 +1146,26 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       const uint32_t aph = (n >> 1) & 1;
       const int grow0 = ti.e * p.M + i * BM;
       const int cur = ti.k & 1;
-      // axpy operand D and output C of this phase
-      const CUtensorMap *md = mode == 1 ? &maps.a128 : &maps.xy128[cur];
-      const CUtensorMap *mc = mode == 0 ? &maps.a128 : (mode == 1 ? &maps.b128 : &maps.xy128[cur ^ 1]);
-      if (elected && mode != 0) {
-        // staging is free: the previous tile's stores were waited for before its completion was signalled
-        fence_proxy_async_all();
-        mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
-        for (int b = 0; b < 2 * nblk; ++b)
-          tma_load_2d(epi_base + b * kEpiBoxBytes, md, j * 128 + b * 64, grow0, dfull_bar);
+      bool ok = true;
+      if (mode != 0) {
+        if (elected) {
+          // the staging tile is free once the previous tile's store has read it out
+          ok = mbar_wait(stg_free_bar, (n & 1u) ^ 1u, abort_flag);
+          if (ok) {
+            const CUtensorMap *md = mode == 1 ? &maps.a128 : &maps.xy128[cur];   // axpy operand
+            fence_proxy_async_all();
+            mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
+            for (int b = 0; b < 2 * nblk; ++b)
+              tma_load_2d(epi_base + b * kEpiBoxBytes, md, j * 128 + b * 64, grow0, dfull_bar);
+          }
+        }
+      } else {
+        ok = mbar_wait(stg_free_bar, (n & 1u) ^ 1u, abort_flag);
       }
-      bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
+      if (ok) ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
       if (ok && mode != 0) ok = mbar_wait(dfull_bar, d_loads & 1, abort_flag);
-      ok = __all_sync(0xFFFFFFFFu, ok);     // the warp-wide TMEM loads below need a converged warp
       if (mode != 0) ++d_loads;
+      ok = __all_sync(0xFFFFFFFFu, ok);     // the warp-wide TMEM loads below need a converged warp
       if (!ok) {
         if (lane == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
       } else {
@@ -1126,24 +1220,17 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
               mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
           }
         }
+        // accumulator fully read: hand the TMEM buffer back, then pass the staging tile (and, by
+        // ordering, this warp's mirrored stores) to the store thread
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
         fence_async_smem();
-      }
-      // staging tile final; every mirrored store of this CTA issued
-      if (epi_bar_or(1, *abort_flag != 0)) break;
-      if (elected) {
-        for (int b = 0; b < 2 * nblk; ++b)
-          tma_store_2d(mc, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
-        bulk_commit();
-        bulk_wait0();               // stores complete (not only read out of staging)
-        fence_proxy_async_all();
-        __threadfence();            // with the barrier above: covers the other threads' mirrored stores too
-        red_release_gpu_add(p.sched + 2 + ti.e, 1u);
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+          mbar_arrive(stg_full_bar);
+        }
       }
     }
-    if (elected) bulk_wait0();
   }
 
   tc_fence_before();
@@ -1424,6 +1511,8 @@ int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uin
   ANC_REQUIRE(total < 0xFFFFFF00ull, "too many tiles");
   p.total_tiles = (uint32_t)total;
   p.spin_limit = spin_limit ? spin_limit : kSpinLimit;
+  p.prefetch = kPrefetchAhead;
+  if (const char *pf = getenv("ANCORA_NS_PREFETCH")) p.prefetch = atoi(pf) < 0 ? 0 : (atoi(pf) > 64 ? 64 : atoi(pf));
   for (int i = 0; i < 3 * steps; ++i) p.coef[i] = coeffs[i];
   uint64_t pairs = (uint64_t)(ctx->sm_count / 2);
   if (total < pairs) pairs = total;

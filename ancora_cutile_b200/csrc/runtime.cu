@@ -1,5 +1,10 @@
 // Context, device memory, events: the plumbing the reference does with
 // cuda.bindings (cuMemAlloc / cuMemcpy* / cuMemFree in _DBuf, _Buf, _GpuArray).
+#ifndef _GNU_SOURCE
+#define _GNU_SOURCE
+#endif
+#include <sched.h>
+#include <stdlib.h>
 #include <string.h>
 #include "anc_internal.h"
 
@@ -175,6 +180,66 @@ int anc_host_alloc(size_t bytes, void **hptr) {
     return ANC_E_NOMEM;
   }
   return ANC_OK;
+}
+
+// CPUs listed in a sysfs cpulist string ("0-13,56-69") into a cpu_set_t; false if none parsed.
+static bool parse_cpulist(const char *s, cpu_set_t *set) {
+  CPU_ZERO(set);
+  bool any = false;
+  while (*s) {
+    char *end = nullptr;
+    long a = strtol(s, &end, 10);
+    if (end == s) break;
+    long b = a;
+    s = end;
+    if (*s == '-') {
+      b = strtol(s + 1, &end, 10);
+      if (end == s + 1) break;
+      s = end;
+    }
+    for (long c = a; c <= b && c < CPU_SETSIZE; ++c) {
+      if (c >= 0) {
+        CPU_SET((int)c, set);
+        any = true;
+      }
+    }
+    while (*s == ',' || *s == ' ' || *s == '\n') ++s;
+  }
+  return any;
+}
+
+int anc_host_alloc_near(int device, size_t bytes, void **hptr) {
+  ANC_REQUIRE(hptr, "hptr is NULL");
+  *hptr = nullptr;
+  // Page-locked memory lands on the NUMA node of the thread that allocates it.  Bind this thread
+  // to the CPUs next to the GPU for the duration of the allocation, so that host<->device copies
+  // do not cross the socket interconnect; any failure on the way falls back to a plain allocation.
+  cpu_set_t saved, local;
+  bool bound = false;
+  char busid[32] = {0};
+  if (sched_getaffinity(0, sizeof(saved), &saved) == 0 &&
+      cudaDeviceGetPCIBusId(busid, (int)sizeof(busid), device) == cudaSuccess) {
+    for (char *c = busid; *c; ++c)
+      if (*c >= 'A' && *c <= 'F') *c = (char)(*c - 'A' + 'a');
+    char path[128];
+    snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/local_cpulist", busid);
+    FILE *f = fopen(path, "r");
+    if (f) {
+      char line[1024] = {0};
+      if (fgets(line, sizeof(line), f) && parse_cpulist(line, &local)) {
+        cpu_set_t both;
+        CPU_AND(&both, &local, &saved);          // stay inside what this process may use
+        if (CPU_COUNT(&both) > 0 && sched_setaffinity(0, sizeof(both), &both) == 0) bound = true;
+      }
+      fclose(f);
+    }
+  } else {
+    cudaGetLastError();
+  }
+  int rc = anc_host_alloc(bytes, hptr);
+  if (rc == ANC_OK && bound && bytes) memset(*hptr, 0, bytes);   // touch while bound
+  if (bound) sched_setaffinity(0, sizeof(saved), &saved);
+  return rc;
 }
 
 int anc_host_free(void *hptr) {

@@ -45,11 +45,13 @@ def fro_normalize(X, recip, E, M, N, eps=1e-7, stream=None, ctx=None):
                                       float(eps), C.c_void_p(stream or None)))
 
 
-def ns_batched(X, A, B, Y, recip, E, M, N, steps, coeffs, eps=1e-7, stream=None, ctx=None):
+def ns_batched(X, A, B, Y, recip, E, M, N, steps, coeffs, eps=1e-7, stream=None, ctx=None, single_launch=True):
+    """single_launch=False forces one launch per phase (same bits)."""
     ctx = ctx or get_context()
-    L.check(L.lib().anc_ns_batched(ctx.handle, dev_ptr(X), dev_ptr(A), dev_ptr(B), dev_ptr(Y),
-                                   dev_ptr(recip), int(E), int(M), int(N), int(steps),
-                                   _coeff_array(coeffs), float(eps), C.c_void_p(stream or None)))
+    L.check(L.lib().anc_ns_batched_ex(ctx.handle, dev_ptr(X), dev_ptr(A), dev_ptr(B), dev_ptr(Y),
+                                      dev_ptr(recip), int(E), int(M), int(N), int(steps),
+                                      _coeff_array(coeffs), float(eps), int(bool(single_launch)),
+                                      C.c_void_p(stream or None)))
 
 
 def grad_accumulate(acc, src=None, g16=None, numel=None, src_dtype="f32", elem_offset=0, scale=1.0,

@@ -7,6 +7,8 @@ Classes and their reference counterparts:
   ResidentMuon     one resident weight over caller-owned p32/p16        muon.py:164-204
   BatchedProjMuon  all resident 2-D weights, batched by NS shape        muon.py:207-284
   MuonScratch      kept for signature parity; the plan owns its scratch muon.py:137-161
+  DeviceMuon       one device-resident weight that owns all its buffers muon.py:88-135
+  ExpertMuonScratch  caller-visible scratch of the batched expert chain ancora/kernels/moe.py:404-421
 
 Coefficients: callers that pass no ``schedule`` get the process-wide default selected by
 ``set_polar_express`` (Keller unless switched on), as in the reference.
@@ -110,6 +112,74 @@ class MuonScratch:
 
     def free(self):
         pass
+
+
+class DeviceMuon:
+    """Device-resident Muon over ONE 2-D weight that owns its buffers (ancora/optim/muon.py:88-135):
+    fp32 master ``p32``, one momentum buffer ``buf``, the bf16 weight ``p16`` the forward reads.
+    ``step(g_dev, si)`` takes the (K,N) float32 device gradient and runs momentum -> Newton-Schulz ->
+    update -> bf16 refresh on the device, asynchronously.  The reference's per-weight scratch
+    (``u, gA, gA2, gB, scr, gBX, recip``) lives inside the plan here."""
+
+    def __init__(self, W, lr=0.02, momentum=0.95, ns_steps=5, grad_dtype="f32", schedule=_UNSET, ctx=None):
+        W = np.asarray(W)
+        assert W.ndim == 2, f"Muon is for 2D matrices, got {W.shape}"
+        K, N = W.shape
+        _check_aligned(K, N)
+        self.ctx = ctx or get_context()
+        self.K, self.N, self.tr = K, N, K > N
+        self.M, self.Nn = (N, K) if self.tr else (K, N)
+        self.lr = lr
+        self.lr_scale = lr * max(1.0, K / N) ** 0.5
+        self.mom, self.ns = momentum, ns_steps
+        w32 = np.ascontiguousarray(W, dtype=np.float32)
+        self.p32 = DBuf(w32, self.ctx)
+        self.p16 = DBuf(f32_to_bf16_bits(w32), self.ctx)
+        self._inner = ResidentMuon(self.p32, self.p16, K, N, None, momentum, ns_steps, grad_dtype=grad_dtype,
+                                   schedule=schedule, ctx=self.ctx)
+        self.buf = self._inner.buf
+
+    def step(self, g_dev, si):
+        self._inner.step(g_dev, si, lr=self.lr)
+
+    def master(self):
+        return self.p32.to_numpy()
+
+    def weights(self):
+        return bits_to_f32(self.p16.to_numpy())
+
+    def free(self):
+        self._inner.free()
+        self.p32.free()
+        self.p16.free()
+
+
+class ExpertMuonScratch:
+    """Scratch of the batched expert Newton-Schulz chain with the reference's attribute names
+    (ancora/kernels/moe.py:404-421): ``u`` (E*M, N) holds the packed momentum input and receives
+    the orthogonalised output, ``gA, gB`` (E*M, M), ``gBX`` (E*M, N), ``recip`` (E, 1); pass them
+    to ``newton_schulz_resident_e(sc.u, sc.gA, sc.gA2, sc.gB, sc.gBX, sc.recip, E, M, N, si)`` as the
+    reference's GroupedMoEFFN.step does (moe.py:583-586).  ``gA2`` is a one-row stand-in: the fused
+    chain never materialises A@A.  N defaults to M (the reference's square experts); rectangular
+    experts pass N explicitly."""
+
+    def __init__(self, E, M, N=None, ctx=None):
+        N = M if N is None else N
+        assert M <= N and M % muon_ns.NTM == 0 and N % muon_ns.NTN == 0, f"expert shape ({M},{N}) tile-misaligned"
+        self.ctx = ctx or get_context()
+        self.E, self.M, self.N = E, M, N
+        Z = lambda *s: DBuf.zeros(s, np.uint16, self.ctx)
+        self.gA, self.gB = Z(E * M, M), Z(E * M, M)
+        self.gA2 = Z(1, 8)
+        self.gBX, self.u = Z(E * M, N), Z(E * M, N)
+        self.recip = DBuf.zeros((E, 1), np.float32, self.ctx)
+
+    def nbytes(self):
+        return sum(b.nbytes for b in (self.gA, self.gA2, self.gB, self.gBX, self.u, self.recip))
+
+    def free(self):
+        for b in (self.gA, self.gA2, self.gB, self.gBX, self.u, self.recip):
+            b.free()
 
 
 class ResidentMuon:

@@ -4,8 +4,10 @@
 lists (muon_ns.py:245,430): packed bf16 operand ``gX`` overwritten with the result,
 caller-owned scratch ``gA, gA2, gB, gBX`` and ``grecip``.  The chain itself runs in the
 library's tcgen05 kernels; ``gA2`` is accepted and left untouched (the fused chain never
-materialises A@A, as in the reference's ``fused=True`` path).  Only the fused chain
-exists here; ``fused=False`` raises.
+materialises A@A, as in the reference's ``fused=True`` path).  ``fused=False``, which in the
+reference selects the chain of separate matmul / axpy launches (muon_ns.py:277-283), here
+selects one launch per phase instead of the single persistent launch; the arithmetic and
+the resulting bits are the same.
 """
 from .kernels import ns_batched
 
@@ -48,20 +50,20 @@ def coeff_list(schedule, steps):
     return [tuple(_coef_at(schedule, k)) for k in range(steps)]
 
 
-def _check(M, N, fused):
+def _check(M, N):
     assert M <= N, f"Newton-Schulz needs M <= N, got ({M},{N}); transpose tall weights first"
     assert M % NTM == 0 and N % NTN == 0, f"NS shape ({M},{N}) tile-misaligned"
-    if not fused:
-        raise NotImplementedError("only the fused Newton-Schulz chain is implemented")
 
 
 def newton_schulz_resident(gX, gA, gA2, gB, gBX, grecip, M, N, si, steps=5, eps=1e-7,
                            schedule=_KELLER, fused=True):
-    _check(M, N, fused)
-    ns_batched(gX, gA, gB, gBX, grecip, 1, M, N, steps, coeff_list(_resolve(schedule), steps), eps, si)
+    _check(M, N)
+    ns_batched(gX, gA, gB, gBX, grecip, 1, M, N, steps, coeff_list(_resolve(schedule), steps), eps, si,
+               single_launch=bool(fused))
 
 
 def newton_schulz_resident_e(gX, gA, gA2, gB, gBX, grecip, E, M, N, si, steps=5, eps=1e-7,
                              schedule=_KELLER, fused=True):
-    _check(M, N, fused)
-    ns_batched(gX, gA, gB, gBX, grecip, E, M, N, steps, coeff_list(_resolve(schedule), steps), eps, si)
+    _check(M, N)
+    ns_batched(gX, gA, gB, gBX, grecip, E, M, N, steps, coeff_list(_resolve(schedule), steps), eps, si,
+               single_launch=bool(fused))

@@ -216,11 +216,7 @@ class ResidentHybrid:
         multi = exchange and self.world > 1
         if multi and self.nccl_overlap:
             # NCCL all-gather of each unit on a second stream as soon as the unit is computed
-            if self._comm_stream is None:
-                st = C.c_void_p()
-                L.check(L.lib().anc_stream_create(self.ctx.handle, C.byref(st)))
-                self._comm_stream = st.value
-            cs = self._comm_stream
+            cs = self._comm_stream_handle()
             if getattr(self, "_overlap_for", None) is not self.units:
                 self._overlap_steps = self.layout.exchange_schedule(
                     ["adamw" if u[0] == "adamw" else u[4] for u in self.units])
@@ -237,11 +233,7 @@ class ResidentHybrid:
                 k += 1
                 ev.record(si)
                 L.check(lib.anc_stream_wait_event(cs, ev.handle))
-                if what == "adamw":
-                    self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, cs)
-                else:
-                    g = self._gmap[what]
-                    self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], cs)
+                self._gather_group(what, cs)
             done = evs[k]
             done.record(cs)
             L.check(lib.anc_stream_wait_event(si, done.handle))
@@ -250,6 +242,25 @@ class ResidentHybrid:
             self._compute_unit(u, si)
         if multi:
             self.exchange(si)
+
+    def step_part(self, kind, si=None, exchange=True):
+        """Only the AdamW units (kind "adamw": advances the step number ``t``) or only the Muon
+        units (kind "muon"), for callers that drive the two sub-optimizers separately as the
+        reference's ``opt.muon.step`` / ``opt.adamw.step`` do (ancora/optim/hybrid.py:45-47)."""
+        assert kind in ("adamw", "muon")
+        si = si or self.ctx.stream
+        if kind == "adamw":
+            self.t += 1
+        for u in self.units:
+            if u[0] == kind:
+                self._compute_unit(u, si)
+        if exchange and self.world > 1:
+            assert self.comm is not None, "world > 1 needs a communicator"
+            if kind == "adamw":
+                self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, si)
+            else:
+                for g in self.groups:
+                    self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], si)
 
     def upload_full_grads(self, grads, si=None):
         """Host -> device copy of ALL gradients (a data-parallel replica's local gradients, to
@@ -323,12 +334,19 @@ class ResidentHybrid:
         step: AdamW's step number and scalars come from device memory (a schedule for the next
         ``horizon`` steps is uploaded here), everything else in the step has fixed arguments.
         Call after at least one eager ``step`` (first calls allocate); hyper-parameters are
-        frozen into the graph."""
+        and the stochastic-rounding seed are frozen into the graph.  The device step counter is
+        mirrored on the host (``_graph_next``): eager steps or ``load_state_dict`` between replays
+        move ``t`` away from it, and ``replay_step`` then points the device counter at ``t + 1``
+        again before launching (or asks for a new capture when that step lies outside the
+        uploaded schedule or the seed changed)."""
         si = si or self.ctx.stream
         a = self.adamw_kw
         self.ctx.sync(si)
         self.adamw.set_schedule(self.t + 1, horizon, a["lr"], a["betas"][0], a["betas"][1], a["eps"])
+        self._graph_first = self.t + 1
         self._graph_limit = self.t + horizon
+        self._graph_next = self.t + 1
+        self._graph_seed = self.seed
         lib = L.lib()
         L.check(lib.anc_graph_begin(self.ctx.handle, si))
         try:
@@ -349,9 +367,19 @@ class ResidentHybrid:
     def replay_step(self, si=None):
         """One optimizer step by replaying the captured graph (asynchronous)."""
         assert getattr(self, "_graph", None), "capture_step first"
-        assert self.t < self._graph_limit, "schedule exhausted: capture_step again"
+        si = si or self.ctx.stream
+        if self.seed != self._graph_seed:
+            raise RuntimeError("the stochastic-rounding seed changed since capture_step: capture again")
+        if not (self._graph_first <= self.t + 1 <= self._graph_limit):
+            raise RuntimeError(f"step {self.t + 1} lies outside the captured schedule "
+                               f"[{self._graph_first}, {self._graph_limit}]: capture_step again")
+        if self._graph_next != self.t + 1:
+            # an eager step or a restored state moved the step number since the last replay
+            self.adamw.set_counter(self.t + 1, si)
+            self._graph_next = self.t + 1
         self.t += 1
-        L.check(L.lib().anc_graph_launch(self.ctx.handle, self._graph, si or self.ctx.stream))
+        self._graph_next += 1
+        L.check(L.lib().anc_graph_launch(self.ctx.handle, self._graph, si))
 
     def exchange(self, si=None):
         """NCCL path: one in-place all-gather per unit."""
@@ -365,8 +393,8 @@ class ResidentHybrid:
         """Page-locked host staging for the gradients, one numpy view per name, laid out like
         the device gradient arenas so that one copy per unit moves everything."""
         if self._pin_g is None:
-            pa = PinnedArray((self.a_padded,), self._gdt)
-            pm = PinnedArray((self.m_total,), self._gdt)
+            pa = PinnedArray((self.a_padded,), self._gdt, self.ctx.device)
+            pm = PinnedArray((self.m_total,), self._gdt, self.ctx.device)
             views = {}
             for n in self.adamw_names + self.muon_names:
                 src = pa if n in self.a_off else pm
@@ -375,9 +403,12 @@ class ResidentHybrid:
             self._pin_g = (pa, pm, views)
         return self._pin_g[2]
 
-    def _stage_grads(self, grads):
+    def _stage_grads(self, grads, names=None):
         views = self.pinned_grads()
-        for n, v in views.items():
+        if grads is views:
+            return                            # the caller filled the staging views themselves
+        for n in (views if names is None else names):
+            v = views[n]
             g = grads[n]
             if isinstance(g, np.ndarray) and g.ctypes.data == v.ctypes.data and g.dtype == v.dtype:
                 continue                      # caller wrote straight into the staging view
@@ -404,14 +435,17 @@ class ResidentHybrid:
                                     stream or None, 0))
         return n * 2
 
-    def upload_grads(self, grads, si=None):
-        """Host -> device copy of this rank's share of the gradients (asynchronous)."""
-        self._stage_grads(grads)
-        return sum(self._h2d_unit(u, si) for u in self.units)
+    def upload_grads(self, grads, si=None, kind=None):
+        """Host -> device copy of this rank's share of the gradients (asynchronous); ``kind``
+        ("adamw" or "muon") restricts it to one sub-optimizer's tensors."""
+        names = None if kind is None else (self.adamw_names if kind == "adamw" else self.muon_names)
+        self._stage_grads(grads, names)
+        return sum(self._h2d_unit(u, si) for u in self.units if kind is None or u[0] == kind)
 
     def _ensure_host_side(self):
         if self._pin_w is None:
-            self._pin_w = (PinnedArray((self.a_padded,), np.uint16), PinnedArray((self.m_total,), np.uint16))
+            self._pin_w = (PinnedArray((self.a_padded,), np.uint16, self.ctx.device),
+                           PinnedArray((self.m_total,), np.uint16, self.ctx.device))
         if self._streams is None:
             ss = []
             for _ in range(2):
@@ -432,29 +466,76 @@ class ResidentHybrid:
             out[n] = src.array[o:o + _numel(self.shapes[n])].reshape(self.shapes[n])
         return out
 
-    def step_host(self, grads, si=None):
+    def _comm_stream_handle(self):
+        if self._comm_stream is None:
+            st = C.c_void_p()
+            L.check(L.lib().anc_stream_create(self.ctx.handle, C.byref(st)))
+            self._comm_stream = st.value
+        return self._comm_stream
+
+    def _gather_group(self, what, stream):
+        """In-place all-gather of one arena group ("adamw" or a Muon shape key) on ``stream``."""
+        if what == "adamw":
+            self.comm.allgather_bf16(self.a_p16.ptr, self.a_per, stream)
+        else:
+            g = self._gmap[what]
+            self.comm.allgather_bf16(self.m_p16.ptr + g["base"] * 2, g["per"], stream)
+
+    def step_host(self, grads, si=None, trace=None):
         """The whole round trip a host-API caller makes, pipelined unit by unit on three
-        streams: gradients host -> device, the step (and, with world > 1, the exchange), this
-        rank's updated bf16 parameters device -> host.  Returns ({name: uint16 view of
-        page-locked memory}, bytes copied in, bytes copied out) after synchronising.
-        With world > 1 only the parameters this rank owns are copied out."""
+        streams: gradients host -> device, the step, this rank's updated bf16 parameters device ->
+        host; with world > 1 each arena group's all-gather is issued on a fourth stream as soon as
+        the group's last unit is computed.  Returns ({name: uint16 view of page-locked memory},
+        bytes copied in, bytes copied out) after synchronising.  With world > 1 only the
+        parameters this rank owns are copied out.
+
+        trace: a dict that receives, in milliseconds from the start of the call on the device
+        clock, when the last upload, the last compute, the last download and the last all-gather
+        finished, plus the host time spent staging and enqueueing."""
+        import time
         si = si or self.ctx.stream
+        t_host0 = time.perf_counter()
         self._ensure_host_side()
         self._stage_grads(grads)
+        t_staged = time.perf_counter()
         s_in, s_out = self._streams
         self.t += 1
         units = self._host_units
         nu = len(units)
-        evs = self._events(3 * nu + 1)
+        multi = self.world > 1
+        if multi:
+            assert self.comm is not None, "world > 1 needs a communicator"
+            if getattr(self, "_host_sched_for", None) is not units:
+                self._host_sched = self.layout.exchange_schedule(
+                    ["adamw" if u[0] == "adamw" else u[4] for u in units])
+                self._host_sched_for = units
+            sched = self._host_sched
+            cs = self._comm_stream_handle()
+        else:
+            sched = [("compute", k) for k in range(nu)]
+            cs = None
+        ng = sum(1 for op in sched if op[0] == "gather")
+        evs = self._events(3 * nu + ng + 8)
         ev_in, ev_c, ev_out = evs[:nu], evs[nu:2 * nu], evs[2 * nu:3 * nu]
-        start = evs[3 * nu]
+        ev_g = evs[3 * nu:3 * nu + ng]
+        start, m_in, m_c, m_out, m_x, end, done_x = evs[3 * nu + ng:3 * nu + ng + 7]
         start.record(si)                       # copies may not overtake work queued earlier on si
         lib = L.lib()
         L.check(lib.anc_stream_wait_event(s_in, start.handle))
         L.check(lib.anc_stream_wait_event(s_out, start.handle))
+        if cs is not None:
+            L.check(lib.anc_stream_wait_event(cs, start.handle))
         h2d = d2h = 0
-        multi = self.world > 1
-        for k, u in enumerate(units):
+        gi = 0
+        for op, what in sched:
+            if op == "gather":
+                ev = ev_g[gi]
+                gi += 1
+                ev.record(si)
+                L.check(lib.anc_stream_wait_event(cs, ev.handle))
+                self._gather_group(what, cs)
+                continue
+            k, u = what, units[what]
             h2d += self._h2d_unit(u, s_in)
             ev_in[k].record(s_in)
             L.check(lib.anc_stream_wait_event(si, ev_in[k].handle))
@@ -463,11 +544,26 @@ class ResidentHybrid:
             L.check(lib.anc_stream_wait_event(s_out, ev_c[k].handle))
             d2h += self._d2h_unit(u, s_out)
             ev_out[k].record(s_out)
-        if multi:
-            self.exchange(si)
-        for k in range(nu):
-            L.check(lib.anc_stream_wait_event(si, ev_out[k].handle))
+        if trace is not None:
+            m_in.record(s_in)
+            m_c.record(si)
+            m_out.record(s_out)
+            if cs is not None:
+                m_x.record(cs)
+        if cs is not None:
+            done_x.record(cs)
+            L.check(lib.anc_stream_wait_event(si, done_x.handle))
+        L.check(lib.anc_stream_wait_event(si, ev_out[nu - 1].handle))   # s_out is in order: the last covers all
+        if trace is not None:
+            end.record(si)
+        t_enq = time.perf_counter()
         self.ctx.sync(si)
+        if trace is not None:
+            trace.update(h2d_done_ms=start.elapsed_ms(m_in), compute_done_ms=start.elapsed_ms(m_c),
+                         d2h_done_ms=start.elapsed_ms(m_out),
+                         exchange_done_ms=start.elapsed_ms(m_x) if cs is not None else None,
+                         total_ms=start.elapsed_ms(end), units=nu,
+                         host_stage_ms=(t_staged - t_host0) * 1e3, host_enqueue_ms=(t_enq - t_staged) * 1e3)
         return self._weight_views(), h2d, d2h
 
     def download_weights_bits(self, si=None, sync=True):

@@ -48,7 +48,7 @@ def moe_family_shapes(n_layers=24, hidden=1024, q_heads=16, kv_heads=8, head_dim
             s[p + "up_proj"] = (hidden, ffn)
             s[p + "down_proj"] = (ffn, hidden)
         else:
-            s[p + "router_head"] = (hidden, experts)       # AdamW: name carries "head"
+            s[p + "router"] = (hidden, experts)            # 2-D but not tileable: AdamW (HybridOptimizer's fallback)
             for e in range(experts):
                 q = p + f"experts.{e}."
                 s[q + "gate_proj"] = (hidden, expert_ffn)

@@ -22,6 +22,13 @@ import sys
 import threading
 import time
 
+# The CPU arm uses every core this process may run on.  Launchers such as torch.distributed.run
+# export OMP_NUM_THREADS=1 to their children, which would cut the BLAS of the CPU arm to one
+# thread; the thread counts are therefore set here, before numpy loads its BLAS.
+if "reference" in sys.argv[1:] or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(len(os.sched_getaffinity(0)))
+
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -103,28 +110,48 @@ def workload_shapes(name, layers=None, vocab=None):
 
 
 def route(shp):
-    from ancora_cutile_b200.hybrid import default_is_muon
-    return [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    from ancora_cutile_b200.hybrid import muon_names_for
+    return muon_names_for(shp)
 
 
 # ------------------------------------------------------------------ CPU arm
-def cpu_sample_step(shp, muon_names, layers=1, adamw_elems=1 << 24):
-    """Builds a bounded sample of the workload for the numpy port: the Muon matrices of the
-    first `layers` layers and `adamw_elems` elements of the embedding.  Returns a callable
-    running one step on it plus the scale factors to the full workload."""
-    from oracle import adamw_ref, muon_ref
+def cpu_arm(shp, muon_names, total_params, steps, warmup, layers):
+    """Times the reference's host optimizer step on this machine's cores.
+
+    Muon: the reference's own host class (ancora/optim/muon.py:287-318, fp32 Newton-Schulz through
+    BLAS) loaded from oracle/_ref when that was built, else the numpy port in oracle/muon_ref.py.
+    AdamW: the reference has no host AdamW class; its kernel's four statements
+    (ancora/optim/adamw.py:34-37) plus the round-to-nearest bf16 cast (:41) are timed through
+    oracle/adamw_ref.py, which equals those statements bit for bit.  The Philox stochastic-rounding
+    pass this build adds is timed separately and is NOT part of the reference's figure.
+
+    A step covers the Muon matrices of the first `layers` layers and the same fraction of the
+    AdamW elements, i.e. a sample with the workload's own composition: the rate in params/s is
+    measured, not extrapolated; only ms_per_step of the whole workload is derived from it.
+    """
+    from oracle import adamw_ref, bf16 as obf, build_ref, muon_ref, philox
+    n_layers = 1 + max(int(n.split(".")[1]) for n in muon_names)
+    layers = min(layers, n_layers)
+    frac = layers / n_layers
     rng = np.random.default_rng(0)
     sel = [n for n in muon_names if int(n.split(".")[1]) < layers]
     P = {n: (rng.standard_normal(shp[n], dtype=np.float32) * np.float32(0.02)) for n in sel}
     G = {n: (rng.standard_normal(shp[n], dtype=np.float32) * np.float32(1e-3)) for n in sel}
-    opt = muon_ref.HostMuon(P, lr=MUON_KW["lr"], momentum=MUON_KW["momentum"], nesterov=True,
-                            ns_steps=MUON_KW["ns_steps"], schedule=muon_ref.PE_SCHEDULE)
-    n = adamw_elems
-    p = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)
-    m = rng.standard_normal(n, dtype=np.float32) * np.float32(1e-4)
-    v = np.abs(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-6))
-    g = rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3)
-    st = {"p": p, "m": m, "v": v, "t": 0}
+    ref = build_ref.load()
+    if ref is not None:
+        opt = ref[0](P, lr=MUON_KW["lr"], momentum=MUON_KW["momentum"], nesterov=True, ns_steps=MUON_KW["ns_steps"])
+        kind, muon_src = "reference", "the reference's host Muon class (oracle/_ref, built from the checkout)"
+    else:
+        opt = muon_ref.HostMuon(P, lr=MUON_KW["lr"], momentum=MUON_KW["momentum"], nesterov=True,
+                                ns_steps=MUON_KW["ns_steps"], schedule=muon_ref.PE_SCHEDULE)
+        kind, muon_src = "port", "numpy port of the reference's host Muon (oracle/_ref not built)"
+    a_total = sum(int(np.prod(s)) for k, s in shp.items() if k not in set(muon_names))
+    n = max(64, int(a_total * frac) // 64 * 64)
+    st = {"p": rng.standard_normal(n, dtype=np.float32) * np.float32(0.02),
+          "m": rng.standard_normal(n, dtype=np.float32) * np.float32(1e-4),
+          "v": np.abs(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-6)), "t": 0}
+    g = obf.rne_f32(rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3))
+    sample_params = sum(int(np.prod(shp[k])) for k in sel) + n
 
     def step():
         t0 = time.perf_counter()
@@ -132,19 +159,11 @@ def cpu_sample_step(shp, muon_names, layers=1, adamw_elems=1 << 24):
         t1 = time.perf_counter()
         st["t"] += 1
         s = adamw_ref.adamw_scalars(ADAMW_KW["lr"], *ADAMW_KW["betas"], ADAMW_KW["eps"], st["t"])
-        st["p"], st["m"], st["v"], _ = adamw_ref.adamw_step(st["p"], st["m"], st["v"], g, s, ADAMW_KW["wd"],
-                                                           "sr", SEED_SR, st["t"], 0)
+        st["p"], st["m"], st["v"] = adamw_ref.adamw_update(st["p"], st["m"], st["v"], g, s, ADAMW_KW["wd"])
+        obf.rne_bits(st["p"])
         t2 = time.perf_counter()
         return t1 - t0, t2 - t1
 
-    from ancora_cutile_b200.zero1 import ns_cost
-    muon_scale = sum(ns_cost(*shp[k]) for k in muon_names) / max(sum(ns_cost(*shp[k]) for k in sel), 1)
-    a_total = sum(int(np.prod(s)) for k, s in shp.items() if k not in set(muon_names))
-    return step, muon_scale, a_total / n, len(sel), n
-
-
-def run_cpu(shp, muon_names, total_params, steps, warmup):
-    step, ms, as_, nsel, n = cpu_sample_step(shp, muon_names)
     for _ in range(warmup):
         step()
     tm = ta = 0.0
@@ -152,12 +171,76 @@ def run_cpu(shp, muon_names, total_params, steps, warmup):
         a, b = step()
         tm += a
         ta += b
-    full_s = (tm * ms + ta * as_) / steps
-    cores = os.cpu_count() or 1
-    sample = (f"numpy port of the reference host step: Muon (fp32 Newton-Schulz, BLAS) on the {nsel} "
-              f"matrices of 1 layer scaled x{ms:.1f} by NS cost, AdamW+SR on {n} embedding elements "
-              f"scaled x{as_:.2f}; {steps} step(s), numpy {np.__version__}")
-    return total_params / full_s, full_s * 1e3, cores, sample
+    t0 = time.perf_counter()
+    obf.sr_bits(st["p"], philox.dither16_range(0, n, SEED_SR, 1))
+    sr_s = time.perf_counter() - t0
+    per_step = (tm + ta) / steps
+    threads = len(os.sched_getaffinity(0))
+    rate = sample_params / per_step
+    return {"value": rate, "unit": "params/s", "cores": threads, "kind": kind,
+            "ms_per_step": total_params / rate * 1e3, "extrapolated": frac < 1.0, "sample_fraction": frac,
+            "sample_params": sample_params, "sample_ms_per_step": per_step * 1e3,
+            "muon_ms": tm / steps * 1e3, "adamw_ms": ta / steps * 1e3,
+            "philox_sr_pass_ms_not_included": sr_s * 1e3,
+            "blas_threads_env": os.environ.get("OMP_NUM_THREADS"),
+            "sample": (f"{muon_src}: {len(sel)} matrices of {layers}/{n_layers} layers; AdamW statements + RNE cast "
+                       f"on {n} elements ({frac:.3f} of the AdamW set): the workload's composition, rate measured on "
+                       f"the sample; {steps} step(s) after {warmup} warm-up, numpy {np.__version__}")}
+
+
+def grad_reduce_scatter_leg(eng, pin, rank, world, ctx):
+    """Rank r's local gradient is bf16(base * (1 + r/16)) for the synthetic base gradient, so every
+    rank can compute the exact sum over ranks for the elements it owns."""
+    from ancora_cutile_b200.bf16 import bits_to_f32, f32_to_bf16_bits
+    base = {n: v.copy() for n, v in pin.items()}
+    scale = lambda r: np.float32(1.0 + r / 16.0)
+    CH = 1 << 24
+
+    def local(bits, r):
+        return f32_to_bf16_bits(bits_to_f32(bits) * scale(r))
+
+    for n, v in pin.items():                          # this rank's local gradients, in the staging views
+        flat, b = v.reshape(-1), base[n].reshape(-1)
+        for lo in range(0, flat.size, CH):
+            flat[lo:lo + CH] = local(b[lo:lo + CH], rank)
+    eng.enable_grad_accumulation()
+    digests, worst, checked, ms = [], 0.0, 0, 0.0
+    e0, e1 = Event_pair()
+    for rep in range(2):
+        eng.upload_full_grads(pin, ctx.stream)
+        e0.record(ctx.stream)
+        eng.finalize_grads(ctx.stream, rounding="rne", reduce=True)
+        e1.record(ctx.stream)
+        ctx.sync()
+        ms = e0.elapsed_ms(e1)
+        import hashlib
+        h = hashlib.blake2b(digest_size=16)
+        for n in pin:
+            lo, hi = eng.owned_range(n)
+            if hi <= lo:
+                continue
+            got = eng.grad_view(n).to_numpy().reshape(-1)[lo:hi]
+            h.update(got.tobytes())
+            if rep == 0:
+                b = base[n].reshape(-1)[lo:hi]
+                for c in range(0, b.size, CH):
+                    want = np.zeros(min(CH, b.size - c), np.float64)
+                    for r in range(world):
+                        want += bits_to_f32(local(b[c:c + CH], r)).astype(np.float64)
+                    want /= world
+                    g = bits_to_f32(got[c:c + CH]).astype(np.float64)
+                    den = np.maximum(np.abs(want), 1e-30)
+                    worst = max(worst, float(np.max(np.abs(g - want) / den)))
+                    checked += want.size
+        digests.append(h.hexdigest())
+    for n, v in pin.items():                          # put the base gradient back
+        np.copyto(v, base[n])
+    return {"max_rel_err": worst, "repeatable_bits": digests[0] == digests[1], "elements_checked": checked, "ms": ms}
+
+
+def Event_pair():
+    import ancora_cutile_b200 as anc
+    return anc.Event(), anc.Event()
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -170,6 +253,7 @@ def main():
     ap.add_argument("--workload", default="qwen3", choices=["qwen3", "moe"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-grad-leg", action="store_true", help="skip the N > 1 gradient reduce-scatter check")
     ap.add_argument("--dump-digests", default=None, help="write per-tensor fingerprints of the bf16 parameters and of the owned float32 masters to this file (rank r > 0: FILE.rankR)")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: fewer layers")
     ap.add_argument("--vocab", type=int, default=None, help="profiling only: smaller vocabulary")
@@ -186,17 +270,25 @@ def main():
               "parallelism": f"zero1x{world}" if world > 1 else "single",
               "l2": "state (7 GB) is far larger than L2; no flush needed"}
 
+    # exchange of the updated bf16 parameters: "nccl_overlap" (default) or "nccl" (after the step)
+    xmode = os.environ.get("ANCORA_EXCHANGE", "nccl_overlap")
+    config["exchange"] = ("none" if world == 1 else ("NCCL all-gather per unit on a second stream"
+                                                     if xmode == "nccl_overlap" else "NCCL all-gather after the step"))
+
     if args.impl == "reference":
         if rank != 0:
             return
-        v, ms, cores, sample = run_cpu(shp, muon_names, total_params, max(args.steps, 1), min(args.warmup, 1))
+        # a whole step when the caller asks for one or two, else a quarter of the layers per step so
+        # that warm-up + steps end within minutes
+        n_layers = 1 + max(int(n.split(".")[1]) for n in muon_names)
+        layers = n_layers if args.steps <= 2 else max(1, n_layers // 4)
+        cb = cpu_arm(shp, muon_names, total_params, max(args.steps, 1), min(args.warmup, 1), layers)
         print(json.dumps({
-            "impl": "reference", "metric": "hybrid_optimizer_step_params_per_s", "value": v, "unit": "params/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config,
-            "cpu_baseline": {"value": v, "unit": "params/s", "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": v, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+            "impl": "reference", "metric": "hybrid_optimizer_step_params_per_s", "value": cb["value"],
+            "unit": "params/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config, "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
     import ancora_cutile_b200 as anc
@@ -241,15 +333,11 @@ def main():
     anc.set_polar_express(True)
     params = S.synthetic_params(shp, seed=0)
     no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
-    # exchange of the updated bf16 parameters: "nccl_overlap" (default) or "nccl" (after the step)
-    xmode = os.environ.get("ANCORA_EXCHANGE", "nccl_overlap")
     eng = anc.ResidentHybrid(params, muon_names, no_decay_names=no_decay, adamw_kw=ADAMW_KW, muon_kw=MUON_KW,
                              grad_dtype="bf16", rounding="sr", seed=SEED_SR, rank=rank, world=world,
                              comm=comm, schedule=anc.PE_SCHEDULE, ctx=ctx)
     del params
     eng.nccl_overlap = world > 1 and xmode == "nccl_overlap"
-    config["exchange"] = ("NCCL all-gather per unit on a second stream" if eng.nccl_overlap
-                          else ("NCCL all-gather after the step" if world > 1 else "none"))
     # synthetic bf16 gradients, written into the page-locked staging views and uploaded once
     pin = eng.pinned_grads()
     S.synthetic_grads_bf16(shp, seed=1, out=pin)
@@ -386,16 +474,39 @@ def main():
         barrier()
         t0 = time.perf_counter()
         e0.record(ctx.stream)
+        traces = []
         for _ in range(args.steps):
-            _, h2d, d2h = eng.step_host(pin, ctx.stream)     # synchronises: the result is on the host
+            tr = {}
+            _, h2d, d2h = eng.step_host(pin, ctx.stream, trace=tr)     # synchronises: the result is on the host
+            traces.append(tr)
         e1.record(ctx.stream)
         barrier()
         wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         e2e_ms = max_over_ranks(max(e0.elapsed_ms(e1) / args.steps, wall_ms))
+        # where one step's time goes on this rank (device clock, ms from the start of the call, mean over
+        # the timed steps): the copies run on their own streams beside the compute stream
+        keys = [k for k in traces[0] if traces[0][k] is not None]
+        brk = {k: float(np.mean([t[k] for t in traces])) for k in keys}
+        brk["pcie_gbs_each_way"] = h2d / (max(brk["h2d_done_ms"], brk["d2h_done_ms"]) * 1e-3) / 1e9
         out["e2e"] = {"value": total_params / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
-                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "breakdown": brk,
                       "api": "HybridOptimizer.step_and_fetch -> ResidentHybrid.step_host: page-locked bf16 "
-                             "gradients in, updated bf16 parameters out, pipelined per unit on 3 streams"}
+                             "gradients in, updated bf16 parameters out, pipelined per unit on 3 streams "
+                             "(+ the NCCL all-gathers on a 4th when N > 1)"}
+    # ---- gradient reduce-scatter feeding the ZeRO-1 owners (N > 1): every rank holds its own local
+    # gradients for all parameters; float32 accumulate -> NCCL reduce-scatter -> bf16 downcast, checked on
+    # every element this rank owns against the float64 sum over ranks, twice for repeatability ----
+    if world > 1 and not args.no_grad_leg:
+        out_rs = grad_reduce_scatter_leg(eng, pin, rank, world, ctx)
+        box = [None] * world
+        dist.all_gather_object(box, out_rs)
+        out["grad_reduce_scatter"] = {
+            "max_rel_err": max(b["max_rel_err"] for b in box), "tolerance": 2.0 ** -8,
+            "repeatable_bits": all(b["repeatable_bits"] for b in box),
+            "elements_checked": sum(b["elements_checked"] for b in box), "ms": max(b["ms"] for b in box),
+            "what": "finalize_grads(reduce=True): bf16 grads -> f32 accumulators -> ncclReduceScatter(f32) -> "
+                    "bf16 RNE of sum/world; compared with the float64 sum of the ranks' gradients"}
+        eng.upload_grads(pin, ctx.stream)     # the step's own gradients again
     # Fingerprint of every updated bf16 parameter, name by name (independent of the arena layout):
     # all ranks must agree, and runs with the same --steps/--warmup at different N print the same
     # value, which is the "bitwise identical to the 1-GPU result" check at full size.
@@ -426,9 +537,8 @@ def main():
     out["device_status"] = status
 
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, ms, cores, sample = run_cpu(shp, muon_names, total_params, 1, 0)
-        out["cpu_baseline"] = {"value": v, "unit": "params/s", "ms_per_step": ms, "cores": cores,
-                               "kind": "port", "sample": sample}
+        n_layers = 1 + max(int(n.split(".")[1]) for n in muon_names)
+        out["cpu_baseline"] = cpu_arm(shp, muon_names, total_params, 1, 0, max(1, n_layers // 4))
     if rank == 0:
         print(json.dumps(out))
     eng.free()

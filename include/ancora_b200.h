@@ -80,6 +80,10 @@ ANC_API int anc_h2d(anc_ctx *ctx, void *dptr, const void *hptr, size_t bytes, vo
 ANC_API int anc_d2h(anc_ctx *ctx, void *hptr, const void *dptr, size_t bytes, void *stream, int sync);
 ANC_API int anc_d2d(anc_ctx *ctx, void *dst, const void *src, size_t bytes, void *stream);
 ANC_API int anc_host_alloc(size_t bytes, void **hptr); /* pinned */
+/* Pinned memory placed on the NUMA node next to `device` (the calling thread is bound to the
+ * GPU's local CPUs while it allocates and touches the pages, then restored); falls back to
+ * anc_host_alloc when the topology cannot be read. */
+ANC_API int anc_host_alloc_near(int device, size_t bytes, void **hptr);
 ANC_API int anc_host_free(void *hptr);
 
 /* CUDA events on the caller's stream (timing in the benchmark). */
@@ -154,6 +158,10 @@ ANC_API int anc_adamw_plan_set_schedule(anc_adamw_plan *plan, const anc_adamw_sc
                                         uint64_t first_step);
 ANC_API int anc_adamw_step_scheduled(anc_adamw_plan *plan, int rounding, uint64_t seed, int advance,
                                      void *stream);
+/* Points the device step counter at `step` (inside the uploaded table) without touching the
+ * table, so a captured graph stays valid after eager steps or a restored state moved the
+ * step number.  Synchronises `stream` first. */
+ANC_API int anc_adamw_plan_set_counter(anc_adamw_plan *plan, uint64_t step, void *stream);
 ANC_API int anc_adamw_plan_destroy(anc_adamw_plan *plan);
 
 /* ------------------------------------------------------------------- Muon ---- */
@@ -246,10 +254,17 @@ ANC_API int anc_muon_plan_destroy(anc_muon_plan *plan);
  * newton_schulz_resident / newton_schulz_resident_e
  * (ancora/kernels/muon_ns.py:245-283,430-468).  X (E*M,N) bf16 bits is overwritten
  * with the result; A,B (E*M,M) and Y (E*M,N) are bf16 scratch; recip (E) f32.
- * M <= N, both multiples of 128.  All buffers 1024-byte aligned. */
+ * M <= N, both multiples of 128.  All buffers 1024-byte aligned.
+ * The whole chain is one persistent launch when M and N are multiples of 256 and
+ * steps <= 16, else one launch per phase; both give the same bits. */
 ANC_API int anc_ns_batched(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y,
                            float *recip, int E, int M, int N, int steps, const float *coeffs,
                            float eps, void *stream);
+/* Same, with the launch structure chosen by the caller: single_launch = 0 always runs one
+ * launch per phase (what the reference's fused=False selects, muon_ns.py:277-283). */
+ANC_API int anc_ns_batched_ex(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint16_t *Y,
+                              float *recip, int E, int M, int N, int steps, const float *coeffs,
+                              float eps, int single_launch, void *stream);
 
 /* One batched GEMM phase of the chain, exposed for kernel-level parity tests
  * (reference kernels: _e_gemm_nt_tril + _e_mirror, _e_gemm_axpy_tril + _e_mirror,

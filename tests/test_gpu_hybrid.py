@@ -194,3 +194,61 @@ def test_graph_replay_equals_eager_steps(ctx):
     for n in shp:
         assert np.array_equal(res[0][0][n], res[1][0][n]), n
         assert np.array_equal(res[0][1][n][2], res[1][1][n][2]), n
+
+
+def test_graph_replay_after_an_eager_step_and_a_restored_state(ctx):
+    """The device step counter follows the host's: capture, eager step, replay must equal four
+    eager steps; a state restored to an earlier step replays from there; a changed seed or a step
+    outside the uploaded schedule asks for a new capture instead of using stale scalars."""
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=14)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    g = S.synthetic_grads_bf16(shp, seed=15)
+
+    def make():
+        eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=5,
+                                 schedule=anc.PE_SCHEDULE, ctx=ctx)
+        eng.upload_grads(g, ctx.stream)
+        return eng
+
+    def snap(eng):
+        ctx.sync()
+        assert ctx.status() == 0
+        bits, _ = eng.download_weights_bits()
+        return {n: b.copy() for n, b in bits.items()}, eng.master()
+
+    ref = make()
+    for _ in range(2):
+        ref.step(ctx.stream)
+    sd2 = ref.state_dict()
+    for _ in range(2):
+        ref.step(ctx.stream)
+    want = snap(ref)
+    ref.free()
+
+    eng = make()
+    eng.step(ctx.stream)
+    eng.capture_step(ctx.stream, horizon=8)
+    eng.replay_step(ctx.stream)            # step 2
+    eng.step(ctx.stream)                   # step 3, eager: the device counter is now behind
+    eng.replay_step(ctx.stream)            # step 4
+    assert eng.t == 4
+    got = snap(eng)
+    for n in shp:
+        assert np.array_equal(got[0][n], want[0][n]) and np.array_equal(got[1][n][2], want[1][n][2]), n
+    eng.load_state_dict(sd2)               # back to the state after step 2
+    eng.replay_step(ctx.stream)
+    eng.replay_step(ctx.stream)
+    assert eng.t == 4
+    got = snap(eng)
+    for n in shp:
+        assert np.array_equal(got[0][n], want[0][n]) and np.array_equal(got[1][n][2], want[1][n][2]), n
+    eng.seed = 6
+    with pytest.raises(RuntimeError):
+        eng.replay_step(ctx.stream)
+    eng.seed = 5
+    eng.t = 100
+    with pytest.raises(RuntimeError):
+        eng.replay_step(ctx.stream)
+    eng.free()

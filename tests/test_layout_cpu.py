@@ -7,13 +7,13 @@ import numpy as np
 import pytest
 
 from ancora_cutile_b200 import shapes as S
-from ancora_cutile_b200.hybrid import default_is_muon
+from ancora_cutile_b200.hybrid import default_is_muon, muon_names_for
 from ancora_cutile_b200.layout import ArenaLayout
 
 
 def _family(which):
     shp = S.qwen3_0_6b_shapes() if which == "qwen3" else S.moe_family_shapes()
-    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    mu = muon_names_for(shp)
     return shp, mu
 
 
@@ -149,7 +149,7 @@ def test_every_rank_enters_the_same_collectives_in_the_same_order(world):
     world 8) and a scratch cap that cuts shares into different numbers of units per rank: the
     gather sequence is the same on every rank, once per arena group, after the rank's own units."""
     shp = S.qwen3_0_6b_shapes(n_layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=4096)
-    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    mu = muon_names_for(shp)
     seqs = []
     for r in range(world):
         lay = ArenaLayout(shp, mu, r, world)
@@ -176,7 +176,7 @@ def test_overlapped_step_issues_that_schedule(monkeypatch):
     from ancora_cutile_b200 import resident
 
     shp = S.qwen3_0_6b_shapes(n_layers=3, hidden=256, q_heads=4, kv_heads=2, head_dim=128, ffn=768, vocab=4096)
-    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    mu = muon_names_for(shp)
 
     class Ev:
         def __init__(self, log):

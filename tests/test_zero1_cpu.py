@@ -6,13 +6,13 @@ import numpy as np
 import pytest
 
 from ancora_cutile_b200 import shapes as S
-from ancora_cutile_b200.hybrid import default_is_muon
+from ancora_cutile_b200.hybrid import default_is_muon, muon_names_for
 from ancora_cutile_b200.zero1 import greedy_partition, ns_cost, slice_bounds
 
 
 def _muon_costs():
     shp = S.qwen3_0_6b_shapes()
-    mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+    mu = muon_names_for(shp)
     return shp, mu, [ns_cost(*shp[n]) for n in mu]
 
 
@@ -79,7 +79,7 @@ def test_two_ranks_agree_and_cover_everything():
 def test_partition_by_group_counts_and_balance(world):
     from ancora_cutile_b200.zero1 import partition_by_group
     for shp in (S.qwen3_0_6b_shapes(), S.moe_family_shapes()):
-        mu = [n for n, s in shp.items() if default_is_muon(n, np.empty((0,) * len(s)))]
+        mu = muon_names_for(shp)
         shapes = [shp[n] for n in mu]
         owner, load = partition_by_group(shapes, world)
         assert owner == partition_by_group(shapes, world)[0]
