@@ -10,18 +10,24 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
-def test_cpu_sample_scales_to_the_full_workload():
+def test_cpu_sample_has_the_workloads_composition():
+    """The CPU arm times a sample with the same Muon / AdamW mix as the whole workload, so its
+    params/s is measured on the sample and only ms_per_step of the full step is derived."""
     import bench
     from ancora_cutile_b200 import shapes as S
     shp = S.qwen3_0_6b_shapes(n_layers=3, hidden=128, q_heads=2, kv_heads=1, head_dim=128, ffn=384, vocab=2048)
     mu = bench.route(shp)
     assert len(mu) == 21
-    step, muon_scale, adamw_scale, nsel, n = bench.cpu_sample_step(shp, mu, layers=1, adamw_elems=1 << 14)
-    assert nsel == 7 and abs(muon_scale - 3.0) < 1e-9                      # 1 of 3 identical layers
-    a_total = sum(int(np.prod(s)) for k, s in shp.items() if k not in set(mu))
-    assert abs(adamw_scale - a_total / (1 << 14)) < 1e-9
-    tm, ta = step()
-    assert tm > 0 and ta > 0
+    total = S.count(shp)
+    cb = bench.cpu_arm(shp, mu, total, steps=1, warmup=0, layers=1)
+    assert cb["extrapolated"] and abs(cb["sample_fraction"] - 1 / 3) < 1e-9          # 1 of 3 identical layers
+    m_total = sum(int(np.prod(shp[n])) for n in mu)
+    a_total = total - m_total
+    assert abs(cb["sample_params"] - (m_total // 3 + a_total / 3)) <= 64            # AdamW share rounded to 64
+    assert cb["kind"] in ("reference", "port") and cb["value"] > 0 and cb["muon_ms"] > 0 and cb["adamw_ms"] > 0
+    assert abs(cb["ms_per_step"] - total / cb["value"] * 1e3) < 1e-6
+    whole = bench.cpu_arm(shp, mu, total, steps=1, warmup=0, layers=3)
+    assert not whole["extrapolated"] and whole["sample_fraction"] == 1.0
 
 
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
@@ -36,5 +42,6 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     for k in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
               "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert k in d, k
-    assert d["impl"] == "reference" and d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["impl"] == "reference" and d["cpu_baseline"]["kind"] in ("reference", "port")
+    assert d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["extrapolated"] is False      # --steps 1: whole step
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["value"] > 0 and d["vs_baseline"] is None
