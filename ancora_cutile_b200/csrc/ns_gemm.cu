@@ -125,6 +125,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -418,12 +428,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar_cluster_addr)
       : "memory");
 }
-// Asks L2 to fetch a box ahead of the load that will bring it into shared memory: the smem ring
-// only covers an L2 hit's latency, so the DRAM latency is taken here, several K blocks earlier.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
   asm volatile(
@@ -466,6 +470,19 @@ __device__ __forceinline__ bool epi_bar_or(int id, bool pred) {
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 p, %2, 0;\n\t"
       "barrier.cta.red.or.pred q, %1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+// The same over the 256 epilogue threads of the chain kernel.
+__device__ __forceinline__ bool epi_bar_or256(int id, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %2, 0;\n\t"
+      "barrier.cta.red.or.pred q, %1, 256, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(r)
       : "r"(id), "r"((uint32_t)pred)
@@ -730,26 +747,39 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // CTA pairs claim tiles with an integer atomicAdd (dynamic scheduling: a pair that starts late,
 // or shares its SMs with another stream's kernel, simply takes fewer tiles).  A tile of matrix
 // e may start when every tile of e's previous phase has been stored, which is tracked by one
-// counter of completed half-tiles per matrix; the same rule makes the reuse of A, B and the
+// completion counter per matrix; the same rule makes the reuse of A, B and the
 // X/Y ping-pong buffers safe.  Tiles are claimed in queue order and only ever depend on
 // earlier tiles, so the smallest unfinished tile can always run: waiting cannot deadlock.
 // The tile -> output mapping and each tile's K order are those of the per-phase kernel, so
 // the results are bitwise the same.
 //
-// Roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-5
-// epilogue, warp 6 scheduler (leader CTA): it claims a tile, waits for the tile's
-// dependencies, decodes it and publishes it to both CTAs through a small ring in shared
-// memory; warp 7 stores the finished staging tile (TMA), waits for the store to complete and
-// then raises the matrix's completion counter, so that latency never sits in the epilogue.
+// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-9
+// epilogue, warp 10 scheduler (leader CTA): it claims a tile, waits for the tile's
+// dependencies, decodes it and publishes it to both CTAs through a small ring in shared memory;
+// warp 11 raises the matrix's completion counter once the 8 epilogue warps have stored their
+// part of a tile (a release at GPU scope waits for the stores to be performed, which would
+// otherwise stall the epilogue for a microsecond per tile).
+//
+// Shared memory holds nothing but the operand ring (7 stages of 32 KiB).  With 256x256 pair
+// tiles the tensor cores read 64 B/clk of operands from shared memory and TMA writes another
+// 64 B/clk into it, which is all the 128 B/clk an SM has; any staging of the epilogue through
+// shared memory therefore takes time from the MMAs, and with K = M = 1024 a tile's epilogue
+// moves a quarter as many bytes as its main loop.  So the epilogue works from registers:
+// each of its 8 warps (two per TMEM lane quarter, one per half of the tile's columns) fetches
+// its rows' 256 bytes of the axpy operand with 256-bit GPU-coherent loads while the tile's MMAs
+// still run, then reads eight 16-column chunks of the accumulator from TMEM (the next chunk in
+// flight while one is combined) and writes the bf16 result with 256-bit stores (full 32-byte
+// sectors).
 // Every wait is bounded; a wait that runs out raises the launch-wide abort word, and all
 // roles drain and return.
 // ====================================================================================
-constexpr int kChainThreads = 256;
-constexpr int kSchedSlots = 3;
-constexpr int kPrefetchAhead = 8;      // K blocks the L2 prefetch runs ahead of the shared-memory load (default)
+constexpr int kChainThreads = 384;
+constexpr int kSchedSlots = 4;
 constexpr int kMaxChainSteps = 16;
+constexpr int kStages3 = 7;
 constexpr uint32_t kTileDone = 0xFFFFFFFFu;
-constexpr int kSmemBytes3 = kStages2 * kStageBytes2 + kEpiBytes + 1024 + 512;
+constexpr int kSmemBytes3 = kStages3 * kStageBytes2 + 1024 + 512;
+constexpr uint32_t kSignalsPerTile = 2;    // one per CTA of the pair
 
 struct alignas(64) ChainMaps {
   CUtensorMap xy128[2];   // the two ping-pong operand buffers, boxes of 64 columns x 128 rows
@@ -758,7 +788,7 @@ struct alignas(64) ChainMaps {
 };
 
 struct ChainParams {
-  uint16_t *A, *B;                     // plain pointers for the mirrored stores
+  uint16_t *XY[2], *A, *B;             // the buffers the epilogue reads and writes directly
   const uint32_t *tab_sym, *tab_full;  // (I | J << 8) per local tile
   const float *mscale;                 // per-matrix Frobenius factor folded into iteration 0 (nullable)
   uint32_t *sched;                     // [0] next tile, [1] abort, [2 + e] completed half-tiles of matrix e
@@ -767,7 +797,6 @@ struct ChainParams {
   int g, a;                            // tiles per matrix in a symmetric phase / in the apply phase
   uint32_t total_tiles;
   uint32_t spin_limit;
-  int prefetch;                        // K blocks of L2 prefetch ahead of the loads (0: none)
   float coef[3 * kMaxChainSteps];
 };
 
@@ -868,28 +897,61 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t *ptr, uint32_t v) {
 // made through the async proxy (TMA) by this thread.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// 256-bit accesses to global memory (eight 32-bit words, 32-byte aligned).  The load is
+// coherent at GPU scope: the data was written by other SMs earlier in this launch, and the same
+// addresses held other values an iteration ago, so it must not be served from this SM's L1.
+__device__ __forceinline__ void ld_gpu_256(const void *ptr, uint32_t (&r)[8]) {
+  asm volatile("ld.relaxed.gpu.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(ptr)
+               : "memory");
+}
+__device__ __forceinline__ void st_256(void *ptr, const uint32_t *r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+// Optional per-role stall accounting (compiled in with -DANC_CHAIN_PROFILE only): every role adds
+// the cycles it spent in each of its waits to a per-CTA row of a device array.
+#ifdef ANC_CHAIN_PROFILE
+__device__ unsigned long long g_chain_prof[512 * 5 * 8];
+#define PROF_BEGIN() unsigned long long _pt = clock64(); unsigned long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_LAP(k)                      \
+  do {                                   \
+    const unsigned long long _n = clock64(); \
+    _pa[k] += _n - _pt;                  \
+    _pt = _n;                            \
+  } while (0)
+#define PROF_END(role)                                                                      \
+  do {                                                                                      \
+    for (int _k = 0; _k < 8; ++_k)                                                          \
+      atomicAdd(&g_chain_prof[((blockIdx.x % 512) * 5 + (role)) * 8 + _k], _pa[_k]);        \
+  } while (0)
+#else
+#define PROF_BEGIN() do { } while (0)
+#define PROF_LAP(k) do { } while (0)
+#define PROF_END(role) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(kChainThreads, 1)
 ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ ChainParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *gen_base = smem_raw + (base - raw);
-  const uint32_t epi_base = base + kStages2 * kStageBytes2;
-  uint8_t *epi_gen = gen_base + kStages2 * kStageBytes2;
-  // after the staging tile: the ring (16-byte slots), then the barriers, then two words
-  const uint32_t ring_addr = epi_base + kEpiBytes;
+  // after the operand ring: the tile ring (16-byte slots), then the barriers, then two words
+  const uint32_t ring_addr = base + kStages3 * kStageBytes2;
   const uint32_t bar0 = ring_addr + 16u * kSchedSlots;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_gen + kEpiBytes + 16 * kSchedSlots);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(gen_base + kStages3 * kStageBytes2 + 16 * kSchedSlots);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages2 + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages2 + 2 + b); };
-  const uint32_t dfull_bar = bar0 + 8u * (2 * kStages2 + 4);      // axpy operand landed in staging
-  const uint32_t stg_full_bar = bar0 + 8u * (2 * kStages2 + 5);   // staging tile final, ready to store
-  const uint32_t stg_free_bar = bar0 + 8u * (2 * kStages2 + 6);   // the store has read staging out
-  auto sfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 7 + s); };                 // tile published
-  auto sempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages2 + 7 + kSchedSlots + s); };  // slot read by all
-  constexpr int kNumBars = 2 * kStages2 + 7 + 2 * kSchedSlots;
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages3 + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages3 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages3 + 2 + b); };
+  auto sfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages3 + 4 + s); };                 // tile published
+  auto sempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages3 + 4 + kSchedSlots + s); };  // slot read by all
+  auto done_bar = [&](int s) { return bar0 + 8u * (2 * kStages3 + 4 + 2 * kSchedSlots + s); };  // tile stored by the 8 warps
+  constexpr int kNumBars = 2 * kStages3 + 4 + 3 * kSchedSlots;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t abort_addr = bar0 + 8u * kNumBars + 4u;
@@ -899,22 +961,20 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
   const uint32_t crank = cluster_ctarank();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages2; ++s) {
+    for (int s = 0; s < kStages3; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 8);
+      mbar_init(tempty_bar(b), 16);   // 8 epilogue warps in each of the 2 CTAs (leader's copy in use)
     }
-    mbar_init(dfull_bar, 1);
-    mbar_init(stg_full_bar, 4);      // one arrival per epilogue warp
-    mbar_init(stg_free_bar, 1);
     for (int s = 0; s < kSchedSlots; ++s) {
       mbar_init(sfull_bar(s), 1);
-      // readers of a slot: the leader's producer, MMA issuer, 4 epilogue warps and store thread (7),
-      // the peer's producer, 4 epilogue warps and store thread (6); the leader's copy is in use
-      mbar_init(sempty_bar(s), 13);
+      // readers of a slot: the leader's producer, MMA issuer, 8 epilogue warps and signaller (11),
+      // the peer's producer, 8 epilogue warps and signaller (10); the leader's copy is in use
+      mbar_init(sempty_bar(s), 21);
+      mbar_init(done_bar(s), 8);     // one arrival per epilogue warp of this CTA
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -942,12 +1002,19 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     st_cluster_u32(map_to_cta(abort_addr, crank ^ 1u), 1u);
     atomicExch(&p.sched[1], 1u);
   };
+  auto release_slot = [&](int slot) {
+    if (crank == 0) mbar_arrive(sempty_bar(slot));
+    else mbar_arrive_cluster(map_to_cta(sempty_bar(slot), 0));
+  };
   // n-th tile of this pair for the calling role; tile.t == kTileDone ends the role.  The
   // scheduler publishes a tile only after its dependency wait (bounded by p.spin_limit), so
   // this wait uses the long fixed bound: it must outlast the scheduler's.
   auto ring_get = [&](uint32_t n, bool arrive, uint32_t bit) -> ChainTile {
     const int slot = (int)(n % kSchedSlots);
-    if (!mbar_wait_cluster(sfull_bar(slot), (n / kSchedSlots) & 1u, abort_flag, kSpinLimit)) {
+    // the leader's roles share a CTA with the scheduler: CTA-scope waits and arrivals do
+    const bool got = crank == 0 ? mbar_wait(sfull_bar(slot), (n / kSchedSlots) & 1u, abort_flag)
+                                : mbar_wait_cluster(sfull_bar(slot), (n / kSchedSlots) & 1u, abort_flag, kSpinLimit);
+    if (!got) {
       if (!*abort_flag) raise_abort(bit);
       ChainTile none;
       none.t = kTileDone;
@@ -955,29 +1022,35 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       return none;
     }
     const ChainTile ti = chain_unpack(ld_shared_v4(ring_addr + 16u * slot));
-    if (arrive) mbar_arrive_cluster(map_to_cta(sempty_bar(slot), 0));
+    if (arrive) release_slot(slot);
     return ti;
   };
 
-  if (warp == 6) {
+  if (warp == 10) {
     // ------------------------------------------------------------ scheduler (leader only)
     if (lane == 0 && crank == 0) {
       const uint32_t limit = p.spin_limit;
-      const uint32_t per_e_it = 2u * (2u * (uint32_t)p.g + (uint32_t)p.a);   // half-tiles per matrix and iteration
+      // completions per matrix and iteration, and before the poly / apply phase of an iteration
+      const uint32_t per_e_it = kSignalsPerTile * (2u * (uint32_t)p.g + (uint32_t)p.a);
+      const uint32_t after_gram = kSignalsPerTile * (uint32_t)p.g;
+      PROF_BEGIN();
       for (uint32_t n = 0;; ++n) {
         const int slot = (int)(n % kSchedSlots);
         ChainTile ti;
         ti.t = kTileDone;
         ti.k = ti.mode = ti.e = ti.I = ti.J = 0;
+        PROF_LAP(0);
         if (mbar_wait_cluster(sempty_bar(slot), ((n / kSchedSlots) & 1u) ^ 1u, abort_flag, kSpinLimit)) {
+          PROF_LAP(1);                 // ring slot free
           const uint32_t t = atomicAdd(&p.sched[0], 1u);
           if (t < p.total_tiles) ti = chain_decode(p, t);
+          PROF_LAP(2);                 // claim + decode
         } else if (!*abort_flag) {
           raise_abort(ANC_DEV_TIMEOUT_DEP);
         }
         if (ti.t != kTileDone) {
           const uint32_t need = (uint32_t)ti.k * per_e_it +
-                                (ti.mode == 1 ? 2u * (uint32_t)p.g : (ti.mode == 2 ? 4u * (uint32_t)p.g : 0u));
+                                (ti.mode == 1 ? after_gram : (ti.mode == 2 ? 2u * after_gram : 0u));
           if (need) {
             const uint32_t *cnt = p.sched + 2 + ti.e;
             bool ready = false;
@@ -995,22 +1068,29 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
             }
           }
         }
+        PROF_LAP(3);                   // dependency wait
         const uint4 w = chain_pack(ti);
-        st_cluster_v4(map_to_cta(ring_addr + 16u * slot, 0), w);
         st_cluster_v4(map_to_cta(ring_addr + 16u * slot, 1), w);
-        mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 0));
         mbar_arrive_cluster(map_to_cta(sfull_bar(slot), 1));
+        asm volatile("st.shared::cta.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(ring_addr + 16u * slot), "r"(w.x),
+                     "r"(w.y), "r"(w.z), "r"(w.w)
+                     : "memory");
+        mbar_arrive(sfull_bar(slot));
         if (ti.t == kTileDone) break;
       }
+      PROF_END(4);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
+      PROF_BEGIN();
       for (uint32_t n = 0;; ++n) {
+        PROF_LAP(0);
         const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_TMA);
+        PROF_LAP(1);                   // waiting for a tile
         if (ti.t == kTileDone) break;
-        fence_proxy_async_all();      // operands come from other CTAs' stores of the previous phase
+        fence_proxy_async_all();      // the operands were written by other SMs' plain stores (previous phase)
         const int cur = ti.k & 1;
         const CUtensorMap *ma = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.b128);
         const CUtensorMap *mb = ti.mode == 0 ? &maps.xy128[cur] : (ti.mode == 1 ? &maps.a128 : &maps.xy64[cur]);
@@ -1019,27 +1099,17 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         const int arow = row0 + ti.I * 256 + (int)crank * 128;
         const int brow = row0 + ti.J * 256 + (int)crank * 128;   // K-major B operand
         const int bcol = ti.J * 256 + (int)crank * 128;          // N-major B operand (apply)
-        auto prefetch = [&](int kb) {
-          tma_prefetch_2d(ma, kb * BK, arow);
-          if (ti.mode != 2) {
-            tma_prefetch_2d(mb, kb * BK, brow);
-          } else {
-            tma_prefetch_2d(mb, bcol, row0 + kb * BK);
-            tma_prefetch_2d(mb, bcol + 64, row0 + kb * BK);
-          }
-        };
-        const int ahead = p.prefetch;
-        for (int kb = 0; kb < ahead && kb < kblocks; ++kb) prefetch(kb);
         bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages2;
-          const uint32_t ph = (it / kStages2) & 1;
-          if (ahead > 0 && kb + ahead < kblocks) prefetch(kb + ahead);
+          const int s = it % kStages3;
+          const uint32_t ph = (it / kStages3) & 1;
+          PROF_LAP(0);
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
             if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_TMA);
             ok = false;
             break;
           }
+          PROF_LAP(2);                 // waiting for a free stage
           const uint32_t sa = base + s * kStageBytes2;
           const uint32_t sb = sa + kABytes;
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
@@ -1054,13 +1124,17 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         }
         if (!ok) break;
       }
+      PROF_END(0);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && crank == 0) {
       uint32_t it = 0;
+      PROF_BEGIN();
       for (uint32_t n = 0;; ++n) {
+        PROF_LAP(0);
         const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_MMA);
+        PROF_LAP(1);                   // waiting for a tile
         if (ti.t == kTileDone) break;
         const bool nmajor_b = (ti.mode == 2);
         const int kblocks = (ti.mode == 0 ? p.N : p.M) / BK;
@@ -1072,17 +1146,20 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
           if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_MMA);
           break;
         }
+        PROF_LAP(2);                   // waiting for a free accumulator (epilogue behind)
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * 256u;
         bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages2;
-          const uint32_t ph = (it / kStages2) & 1;
+          const int s = it % kStages3;
+          const uint32_t ph = (it / kStages3) & 1;
+          PROF_LAP(0);
           if (!mbar_wait(full_bar(s), ph, abort_flag)) {
             if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_MMA);
             ok = false;
             break;
           }
+          PROF_LAP(3);                 // waiting for operands
           tc_fence_after();
           const uint32_t sa = base + s * kStageBytes2;
           const uint32_t sb = sa + kABytes;
@@ -1098,80 +1175,85 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         if (!ok) break;
         tc_commit_pair(tfull_bar(buf));
       }
+      PROF_END(1);
     }
-  } else if (warp == 7) {
-    // ------------------------------------------------------------ store + completion signal (both CTAs)
+  } else if (warp == 11) {
+    // ------------------------------------------------------------ completion signal (both CTAs)
     if (lane == 0) {
+      PROF_BEGIN();
       for (uint32_t n = 0;; ++n) {
-        const ChainTile ti = ring_get(n, true, ANC_DEV_TIMEOUT_EPI);
-        if (ti.t == kTileDone) break;
-        const int i = 2 * ti.I + (int)crank;
-        const int j = 2 * ti.J;
-        const int nblk = (ti.mode == 2 || j + 1 <= i) ? 2 : 1;
-        const int grow0 = ti.e * p.M + i * BM;
-        const int cur = ti.k & 1;
-        const CUtensorMap *mc = ti.mode == 0 ? &maps.a128 : (ti.mode == 1 ? &maps.b128 : &maps.xy128[cur ^ 1]);
-        if (!mbar_wait(stg_full_bar, n & 1u, abort_flag)) {
+        PROF_LAP(0);
+        const ChainTile ti = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
+        PROF_LAP(1);
+        if (ti.t == kTileDone) {
+          release_slot((int)(n % kSchedSlots));
+          break;
+        }
+        // The done barriers are indexed like the ring, and this thread gives its ring slot back only
+        // after the wait: tile n + kSchedSlots cannot be published (so no warp can arrive for it on
+        // the same barrier) before tile n's phase of the barrier has been observed here.
+        if (!mbar_wait(done_bar((int)(n % kSchedSlots)), (n / kSchedSlots) & 1u, abort_flag)) {
           if (!*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
           break;
         }
-        for (int b = 0; b < 2 * nblk; ++b)
-          tma_store_2d(mc, j * 128 + b * 64, grow0, epi_base + b * kEpiBoxBytes);
-        bulk_commit();
-        bulk_wait_read0();            // staging read out: the epilogue may write it again
-        mbar_arrive(stg_free_bar);
-        bulk_wait0();                 // stores complete
+        release_slot((int)(n % kSchedSlots));
+        PROF_LAP(2);                  // waiting for the epilogue warps
+        // release at GPU scope: covers, through the barrier this thread acquired, the stores of all
+        // epilogue threads of this CTA; the next phase reads them through TMA (async proxy)
         fence_proxy_async_all();
-        __threadfence();              // also covers the epilogue threads' mirrored stores (ordered by stg_full)
         red_release_gpu_add(p.sched + 2 + ti.e, 1u);
+        PROF_LAP(3);                  // the release
       }
-      bulk_wait0();
+      PROF_END(3);
     }
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps, both CTAs)
+    // ------------------------------------------------------------ epilogue (8 warps, both CTAs)
+    // Warp w reads TMEM lanes [32 (w & 3), +32) (the only ones it may touch) and, of the tile's
+    // 256 columns, the half (w - 2) / 4, as eight 16-column chunks.  Thread = row.  The axpy
+    // operand of the whole half-row (256 bytes) is requested before the wait for the accumulator.
     const int q = warp & 3;
     const int r = q * 32 + lane;
-    const bool elected = (threadIdx.x == 64);
-    uint32_t d_loads = 0;            // tiles so far that fetched an axpy operand (parity of dfull_bar)
+    const int half = (warp - 2) >> 2;
+    PROF_BEGIN();
     for (uint32_t n = 0;; ++n) {
+      PROF_LAP(0);
       const ChainTile ti = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
-      __syncwarp();                 // every lane has read the slot before the warp releases it
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(sempty_bar((int)(n % kSchedSlots)), 0));
-      if (epi_bar_or(2, ti.t == kTileDone)) break;      // uniform over the 128 threads
+      PROF_LAP(1);                  // waiting for a tile
+      // warp-uniform end of the role (a lane that gave up on the wait must take its warp along:
+      // the TMEM loads below are warp-wide)
+      if (__any_sync(0xFFFFFFFFu, ti.t == kTileDone)) break;
+      const int slot = (int)(n % kSchedSlots);
+      if (lane == 0) release_slot(slot);       // after the vote: every lane has read the slot
       const int mode = ti.mode;
       const int i = 2 * ti.I + (int)crank;
       const int j = 2 * ti.J;
       const int nblk = (mode == 2 || j + 1 <= i) ? 2 : 1;
+      const bool active = half < nblk;    // a diagonal tile's upper block comes from the mirror
       const uint32_t buf = n & 1;
       const uint32_t aph = (n >> 1) & 1;
-      const int grow0 = ti.e * p.M + i * BM;
       const int cur = ti.k & 1;
-      bool ok = true;
-      if (mode != 0) {
-        if (elected) {
-          // the staging tile is free once the previous tile's store has read it out
-          ok = mbar_wait(stg_free_bar, (n & 1u) ^ 1u, abort_flag);
-          if (ok) {
-            const CUtensorMap *md = mode == 1 ? &maps.a128 : &maps.xy128[cur];   // axpy operand
-            fence_proxy_async_all();
-            mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
-            for (int b = 0; b < 2 * nblk; ++b)
-              tma_load_2d(epi_base + b * kEpiBoxBytes, md, j * 128 + b * 64, grow0, dfull_bar);
-          }
-        }
-      } else {
-        ok = mbar_wait(stg_free_bar, (n & 1u) ^ 1u, abort_flag);
+      const int ld = mode == 2 ? p.N : p.M;                                   // row pitch of C and D
+      const uint16_t *dbase = mode == 1 ? p.A : p.XY[cur];                    // axpy operand (modes 1, 2)
+      uint16_t *cbase = mode == 0 ? p.A : (mode == 1 ? p.B : p.XY[cur ^ 1]);
+      const size_t row_off = ((size_t)ti.e * p.M + (size_t)i * BM + r) * ld + (size_t)j * 128 + (size_t)half * 128;
+      const uint16_t *drow = dbase + row_off;
+      uint16_t *crow = cbase + row_off;
+      uint32_t d[64];                     // the half-row of the axpy operand: 128 bf16
+      if (mode != 0 && active) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) ld_gpu_256(drow + s * 16, reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
       }
-      if (ok) ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
-      if (ok && mode != 0) ok = mbar_wait(dfull_bar, d_loads & 1, abort_flag);
-      if (mode != 0) ++d_loads;
-      ok = __all_sync(0xFFFFFFFFu, ok);     // the warp-wide TMEM loads below need a converged warp
+      PROF_LAP(2);                  // issuing the axpy operand loads
+      bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
+      PROF_LAP(3);                  // waiting for the accumulator (MMA-bound when large)
+      ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) {
         if (lane == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
-      } else {
-        tc_fence_after();
-        const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
-        uint8_t *my_row = epi_gen + r * 128;
+        break;
+      }
+      tc_fence_after();
+      if (active) {
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u + (uint32_t)half * 128u;
         const bool scaled = p.mscale != nullptr && ti.k == 0 && mode != 1;
         const float sc = scaled ? p.mscale[ti.e] : 1.f;
         const float sc2 = __fmul_rn(sc, sc);
@@ -1179,58 +1261,53 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         const float beta = mode == 1 ? p.coef[3 * ti.k + 2] : 1.f;
         const float al = scaled ? __fmul_rn(alpha, sc) : alpha;
         const float be = scaled ? __fmul_rn(beta, sc) : beta;
-        uint16_t *cmir = mode == 0 ? p.A : p.B;
-        for (int cc = 0; cc < 4 * nblk; ++cc) {
-          uint32_t v[32];
-          tc_ld32(taddr0 + cc * 32, v);
-          tc_wait_ld();
-          uint8_t *box_row = my_row + (cc >> 1) * kEpiBoxBytes;
-          const int c16 = (cc & 1) * 4;
-          uint32_t h[16];
+        const bool mirror = mode != 2 && j + half < i;   // block (i, j + half) also lands, transposed, at (j + half, i)
+        uint16_t *mcol0 = cbase + ((size_t)ti.e * p.M + (size_t)(j + half) * 128) * p.M + (size_t)i * BM + r;
+        uint32_t va[16], vb[16];
+        tc_ld16(taddr0, va);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            uint4 *slot = reinterpret_cast<uint4 *>(box_row + (((c16 + k4) ^ (r & 7)) << 4));
-            float f[8];
-            if (mode == 0) {
+        for (int s = 0; s < 8; ++s) {
+          uint32_t(&v)[16] = (s & 1) ? vb : va;
+          uint32_t(&vnext)[16] = (s & 1) ? va : vb;
+          tc_wait_ld();                                       // chunk s has landed
+          if (s < 7) tc_ld16(taddr0 + (s + 1) * 16, vnext);    // chunk s + 1 loads while s is processed
+          uint32_t h[8];
+          if (mode == 0) {
 #pragma unroll
-              for (int k = 0; k < 8; ++k)
-                f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k4 * 8 + k])) : __uint_as_float(v[k4 * 8 + k]);
-            } else {
-              const uint4 d = *slot;
-              const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const float dlo = __uint_as_float(dw[k] << 16);
-                const float dhi = __uint_as_float(dw[k] & 0xFFFF0000u);
-                f[2 * k] = __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k]), __fmul_rn(al, dlo));
-                f[2 * k + 1] =
-                    __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
-              }
+            for (int k = 0; k < 8; ++k) {
+              const float lo = __uint_as_float(v[2 * k]), hi = __uint_as_float(v[2 * k + 1]);
+              h[k] = scaled ? pack_bf16(__fmul_rn(sc2, lo), __fmul_rn(sc2, hi)) : pack_bf16(lo, hi);
             }
+          } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) h[k4 * 4 + k] = pack_bf16(f[2 * k], f[2 * k + 1]);
-            *slot = make_uint4(h[k4 * 4], h[k4 * 4 + 1], h[k4 * 4 + 2], h[k4 * 4 + 3]);
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t dw = d[s * 8 + k];
+              const float dlo = __uint_as_float(dw << 16);
+              const float dhi = __uint_as_float(dw & 0xFFFF0000u);
+              h[k] = pack_bf16(__fmaf_rn(be, __uint_as_float(v[2 * k]), __fmul_rn(al, dlo)),
+                               __fmaf_rn(be, __uint_as_float(v[2 * k + 1]), __fmul_rn(al, dhi)));
+            }
           }
-          const int hb = j + (cc >> 2);
-          if (mode != 2 && hb < i) {
-            const int col = j * 128 + cc * 32;
-            uint16_t *mcol = cmir + ((size_t)ti.e * p.M + (size_t)col) * p.M + (size_t)i * BM + r;
+          st_256(crow + s * 16, h);
+          if (mirror) {
+            uint16_t *mcol = mcol0 + (size_t)(s * 16) * p.M;
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
+            for (int k = 0; k < 16; ++k)
               mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
           }
         }
-        // accumulator fully read: hand the TMEM buffer back, then pass the staging tile (and, by
-        // ordering, this warp's mirrored stores) to the store thread
-        tc_fence_before();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
-          mbar_arrive(stg_full_bar);
-        }
       }
+      // accumulator read: hand the TMEM buffer back; then pass this warp's part of the tile to the
+      // signalling thread (the barrier orders the stores of all lanes before its release)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        mbar_arrive(done_bar(slot));
+      }
+      PROF_LAP(5);                  // TMEM -> registers -> global (+ mirrored stores)
     }
+    if (threadIdx.x == 64) PROF_END(2);
   }
 
   tc_fence_before();
@@ -1494,6 +1571,8 @@ int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uin
   }
   ChainParams p;
   memset(&p, 0, sizeof(p));
+  p.XY[0] = X;
+  p.XY[1] = Y;
   p.A = A;
   p.B = B;
   p.tab_sym = ts.d_tab;
@@ -1511,8 +1590,6 @@ int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uin
   ANC_REQUIRE(total < 0xFFFFFF00ull, "too many tiles");
   p.total_tiles = (uint32_t)total;
   p.spin_limit = spin_limit ? spin_limit : kSpinLimit;
-  p.prefetch = kPrefetchAhead;
-  if (const char *pf = getenv("ANCORA_NS_PREFETCH")) p.prefetch = atoi(pf) < 0 ? 0 : (atoi(pf) > 64 ? 64 : atoi(pf));
   for (int i = 0; i < 3 * steps; ++i) p.coef[i] = coeffs[i];
   uint64_t pairs = (uint64_t)(ctx->sm_count / 2);
   if (total < pairs) pairs = total;
@@ -1571,3 +1648,17 @@ extern "C" int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit) {
   if (e != cudaSuccess) return anc_cuda_fail(e, "selftest sync");
   return ANC_OK;
 }
+
+#ifdef ANC_CHAIN_PROFILE
+// Reads (and clears) the stall counters: rows of 8 counters for (CTA, role), roles 0 producer,
+// 1 MMA issuer, 2 epilogue (its elected thread), 3 store thread, 4 scheduler.
+extern "C" __attribute__((visibility("default"))) int anc_debug_chain_prof(unsigned long long *out, int n_ctas) {
+  const size_t bytes = (size_t)n_ctas * 5 * 8 * sizeof(unsigned long long);
+  ANC_CUDA(cudaDeviceSynchronize());
+  ANC_CUDA(cudaMemcpyFromSymbol(out, g_chain_prof, bytes));
+  void *sym = nullptr;
+  ANC_CUDA(cudaGetSymbolAddress(&sym, g_chain_prof));
+  ANC_CUDA(cudaMemset(sym, 0, sizeof(g_chain_prof)));
+  return ANC_OK;
+}
+#endif

@@ -278,3 +278,31 @@ def test_random_models_keep_the_layout_invariants():
         assert all(g == gathers[0] for g in gathers) and len(gathers[0]) == 1 + len(a.groups)
 
     check()
+
+
+def test_routing_of_the_two_model_families():
+    """Muon takes the tileable 2-D hidden matrices only: the MoE router (1024, 16) is 2-D and passes
+    the reference's name rule (ancora/optim/hybrid.py:18-25) but cannot be tiled by 128, so it is
+    stepped by AdamW; BASELINE config 5 counts 576 expert matrices of 768x1024."""
+    q = S.qwen3_0_6b_shapes()
+    mq = muon_names_for(q)
+    assert len(mq) == 196 and sum(int(np.prod(q[n])) for n in q if n not in set(mq)) == 155_648_000
+    m = S.moe_family_shapes()
+    mm = muon_names_for(m)
+    routers = [n for n in m if n.endswith(".router")]
+    assert len(routers) == 12 and all(m[n] == (1024, 16) for n in routers)
+    assert all(default_is_muon(n, np.empty((0, 0))) for n in routers)      # the name rule alone says Muon
+    assert not set(routers) & set(mm)                                       # the tiling rule sends them to AdamW
+    experts = [n for n in mm if ".experts." in n]
+    assert len(experts) == 576 and all(sorted(m[n]) == [768, 1024] for n in experts)
+    assert len(mm) == 576 + 24 * 4 + 12 * 3
+    # the hybrid step host schedule: every rank gathers the same groups in the same order
+    for world in (1, 8):
+        orders = []
+        for r in range(world):
+            lay = ArenaLayout(m, mm, r, world)
+            units = lay.make_units(None, 32 << 20)
+            sched = lay.exchange_schedule(["adamw" if u[0] == "adamw" else u[1] for u in units])
+            orders.append([w for op, w in sched if op == "gather"])
+            assert [w for op, w in sched if op == "compute"] == list(range(len(units)))
+        assert all(o == orders[0] for o in orders)
