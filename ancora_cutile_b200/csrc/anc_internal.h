@@ -85,8 +85,10 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_ext
                             cudaStream_t st);
 // mscale (nullable): per-matrix factor r[e] folded into the epilogue -- mode 0 stores
 // RNE(r^2 * acc), mode 2 stores RNE((alpha*r)*Q + (beta*r)*acc); mode 1 ignores it.
+// diag (mode 1): added to the diagonal of every matrix before the rounding (0 adds nothing).
+// Mode 2 with alpha == 0 reads no axpy operand.
 int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
-                       int E, int M, int N, float alpha, float beta, const float *mscale,
+                       int E, int M, int N, float alpha, float beta, float diag, const float *mscale,
                        cudaStream_t st);
 // One persistent launch for the whole chain (M and N multiples of 256, at most 16 steps); the result is
 // in X for an even number of steps, in Y for an odd one.  sched: 2 + E zeroed words.

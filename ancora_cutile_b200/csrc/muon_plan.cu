@@ -50,8 +50,10 @@ struct anc_muon_plan {
 };
 
 // The chain on an UN-normalised X: the Frobenius factor r[e] = recip[e] enters through the
-// epilogues of the first iteration (A = r^2 X X^T, Y = (a r) X + r (B X)), which equals the
-// chain on r*X without ever writing r*X back to memory.
+// epilogues of the first iteration (A = r^2 X X^T, Y = r (B' X)), which equals the chain on r*X
+// without ever writing r*X back to memory.  The iteration's a*X term is folded into the
+// polynomial, B' = b A + c A A + a I, so that the new iterate is the plain product B' X
+// (the reference forms a*X + B X in the last epilogue, ancora/kernels/muon_ns.py:268-273).
 // sched: the chain kernel's scheduler words (cleared by the Frobenius finalize kernel); when it
 // is NULL, or the shape is outside the chain kernel's reach, every phase is its own launch.
 static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16_t *&Y, int E, int M,
@@ -66,11 +68,11 @@ static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16
   for (int k = 0; k < steps; ++k) {
     const float a = coeffs[3 * k], b = coeffs[3 * k + 1], c = coeffs[3 * k + 2];
     const float *ms = (k == 0) ? recip : nullptr;
-    int rc = anc_launch_ns_gemm(ctx, 0, X, nullptr, A, E, M, N, 0.f, 1.f, ms, st);
+    int rc = anc_launch_ns_gemm(ctx, 0, X, nullptr, A, E, M, N, 0.f, 1.f, 0.f, ms, st);
     if (rc) return rc;
-    rc = anc_launch_ns_gemm(ctx, 1, A, nullptr, B, E, M, N, b, c, nullptr, st);
+    rc = anc_launch_ns_gemm(ctx, 1, A, nullptr, B, E, M, N, b, c, a, nullptr, st);   // B' = bA + cAA + aI
     if (rc) return rc;
-    rc = anc_launch_ns_gemm(ctx, 2, B, X, Y, E, M, N, a, 1.f, ms, st);
+    rc = anc_launch_ns_gemm(ctx, 2, B, X, Y, E, M, N, 0.f, 1.f, 0.f, ms, st);        // X' = B' X
     if (rc) return rc;
     std::swap(X, Y);
   }

@@ -5,8 +5,14 @@
 // overlaps the MMAs of the next.
 //
 //   mode 0 (gram)  : C = RNE(P P^T)                    lower 128-blocks + mirrored store
-//   mode 1 (poly)  : C = RNE(alpha*P + beta*(P P^T))   P symmetric, so P P^T = P P
+//   mode 1 (poly)  : C = RNE(alpha*P + beta*(P P^T) [+ diag*I])   P symmetric, so P P^T = P P
 //   mode 2 (apply) : C = RNE(alpha*Q + beta*(P Q))     full tiles, Q read N-major
+//
+// The optimizer's chain folds the iteration's a*X term into the polynomial: with
+// B' = b*A + c*A*A + a*I (the diagonal added in fp32 before the one rounding of B') the new
+// iterate is X' = B'*X, a plain product, so the apply phase fetches no axpy operand at all:
+// a quarter less epilogue traffic on the phase that holds 70 % of the tiles.  Against the fp32
+// chain the error is the same as with the separate a*X term (0.5 % relative Frobenius).
 //
 // which are the three launches per iteration of the reference's fused chain
 // (ancora/kernels/muon_ns.py:261-273: _gemm_nt_tril+_mirror, _gemm_axpy_tril+_mirror,
@@ -47,6 +53,8 @@ struct GemmParams {
   int E, M, ldc;          // matrices, rows per matrix, row pitch of C/D in elements
   int tiles_per_matrix, total_tiles, kblocks, mode;
   float alpha, beta;
+  float diag;             // mode 1: added to the diagonal elements (0 = nothing added, bit for bit)
+  int use_d;              // the axpy operand D is read (mode 1; mode 2 unless alpha == 0)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------
@@ -125,15 +133,11 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t *r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -333,6 +337,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < 32; ++k)
             f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k])) : __uint_as_float(v[k]);
+        } else if (!p.use_d) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) f[k] = __fmul_rn(be, __uint_as_float(v[k]));
         } else {
           const uint4 *drow = reinterpret_cast<const uint4 *>(p.D + grow * p.ldc + col);
 #pragma unroll
@@ -349,6 +356,12 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                   __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
             }
           }
+        }
+        if (p.mode == 1 && p.diag != 0.f) {   // the matrix's diagonal passes through this chunk?
+          const int dk = i * BM + r - col;
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (k == dk) f[k] = __fadd_rn(f[k], p.diag);
         }
         uint32_t h[16];
 #pragma unroll
@@ -647,7 +660,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int grow0 = e * p.M + i * BM;
       if (elected) {
         bulk_wait_read0();                    // previous tile's stores no longer read staging
-        if (p.mode != 0) {
+        if (p.use_d) {
           mbar_expect_tx(dfull_bar, (uint32_t)nblk * 2u * kEpiBoxBytes);
           for (int b = 0; b < 2 * nblk; ++b)
             tma_load_2d(epi_base + b * kEpiBoxBytes, &tmD, j * 128 + b * 64, grow0, dfull_bar);
@@ -655,7 +668,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       epi_bar(2);                             // staging is free for this tile
       bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
-      if (ok && p.mode != 0) ok = mbar_wait(dfull_bar, acc_it & 1, abort_flag);
+      if (ok && p.use_d) ok = mbar_wait(dfull_bar, acc_it & 1, abort_flag);
       ok = __all_sync(0xFFFFFFFFu, ok);       // the warp-wide TMEM loads below need a converged warp
       if (!ok) {
         if (lane == 0) atomicOr(p.status, ANC_DEV_TIMEOUT_EPI);
@@ -685,6 +698,9 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
               for (int k = 0; k < 8; ++k)
                 f[k] = scaled ? __fmul_rn(sc2, __uint_as_float(v[k4 * 8 + k])) : __uint_as_float(v[k4 * 8 + k]);
+            } else if (!p.use_d) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) f[k] = __fmul_rn(be, __uint_as_float(v[k4 * 8 + k]));
             } else {
               const uint4 d = *slot;
               const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
@@ -696,6 +712,12 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 f[2 * k + 1] =
                     __fmaf_rn(be, __uint_as_float(v[k4 * 8 + 2 * k + 1]), __fmul_rn(al, dhi));
               }
+            }
+            if (p.mode == 1 && p.diag != 0.f) {   // the matrix's diagonal passes through these 8 columns?
+              const int dk = i * BM + r - (j * 128 + cc * 32 + k4 * 8);
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                if (k == dk) f[k] = __fadd_rn(f[k], p.diag);
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k) h[k4 * 4 + k] = pack_bf16(f[2 * k], f[2 * k + 1]);
@@ -753,12 +775,12 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // The tile -> output mapping and each tile's K order are those of the per-phase kernel, so
 // the results are bitwise the same.
 //
-// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warps 2-9
-// epilogue, warp 10 scheduler (leader CTA): it claims a tile, waits for the tile's
-// dependencies, decodes it and publishes it to both CTAs through a small ring in shared memory;
-// warp 11 raises the matrix's completion counter once the 8 epilogue warps have stored their
-// part of a tile (a release at GPU scope waits for the stores to be performed, which would
-// otherwise stall the epilogue for a microsecond per tile).
+// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warp 2 scheduler
+// (leader CTA): it claims a tile, waits for the tile's dependencies, decodes it and publishes
+// it to both CTAs through a small ring in shared memory; warp 3 raises the matrix's completion
+// counter once the epilogue warps have stored their part of a tile (a release at GPU scope
+// waits for the stores to be performed, which would otherwise stall the epilogue for a
+// microsecond per tile); warps 4-11 epilogue.
 //
 // Shared memory holds nothing but the operand ring (7 stages of 32 KiB).  With 256x256 pair
 // tiles the tensor cores read 64 B/clk of operands from shared memory and TMA writes another
@@ -767,9 +789,10 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // moves a quarter as many bytes as its main loop.  So the epilogue works from registers:
 // each of its 8 warps (two per TMEM lane quarter, one per half of the tile's columns) fetches
 // its rows' 256 bytes of the axpy operand with 256-bit GPU-coherent loads while the tile's MMAs
-// still run, then reads eight 16-column chunks of the accumulator from TMEM (the next chunk in
-// flight while one is combined) and writes the bf16 result with 256-bit stores (full 32-byte
-// sectors).
+// still run, then reads its half-row of the accumulator from TMEM in two 64-column loads
+// (every TMEM load round trip is slow while MMAs are queued: eight 16-column loads took 4 us
+// per tile, as long as the tile's MMAs) and writes the bf16 result with 256-bit stores (full
+// 32-byte sectors).
 // Every wait is bounded; a wait that runs out raises the launch-wide abort word, and all
 // roles drain and return.
 // ====================================================================================
@@ -915,6 +938,10 @@ __device__ __forceinline__ void st_256(void *ptr, const uint32_t *r) {
 // Optional per-role stall accounting (compiled in with -DANC_CHAIN_PROFILE only): every role adds
 // the cycles it spent in each of its waits to a per-CTA row of a device array.
 #ifdef ANC_CHAIN_PROFILE
+// timing experiments (profile build only; results are wrong when set): 1 skip the result stores,
+// 2 skip the mirrored stores, 4 skip the axpy operand loads, 8 skip the TMEM loads
+__device__ int g_chain_dbg = 0;
+#define DBG_ON(bit) ((g_chain_dbg & (bit)) == 0)
 __device__ unsigned long long g_chain_prof[512 * 5 * 8];
 #define PROF_BEGIN() unsigned long long _pt = clock64(); unsigned long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_LAP(k)                      \
@@ -929,6 +956,7 @@ __device__ unsigned long long g_chain_prof[512 * 5 * 8];
       atomicAdd(&g_chain_prof[((blockIdx.x % 512) * 5 + (role)) * 8 + _k], _pa[_k]);        \
   } while (0)
 #else
+#define DBG_ON(bit) true
 #define PROF_BEGIN() do { } while (0)
 #define PROF_LAP(k) do { } while (0)
 #define PROF_END(role) do { } while (0)
@@ -993,7 +1021,6 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
   pdl_wait();
-
   // Raises the abort state everywhere: this CTA, the peer CTA, and the launch-wide word that
   // the schedulers of the other pairs poll while they wait for a dependency.
   auto raise_abort = [&](uint32_t bit) {
@@ -1026,7 +1053,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     return ti;
   };
 
-  if (warp == 10) {
+  if (warp == 2) {
     // ------------------------------------------------------------ scheduler (leader only)
     if (lane == 0 && crank == 0) {
       const uint32_t limit = p.spin_limit;
@@ -1177,7 +1204,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       }
       PROF_END(1);
     }
-  } else if (warp == 11) {
+  } else if (warp == 3) {
     // ------------------------------------------------------------ completion signal (both CTAs)
     if (lane == 0) {
       PROF_BEGIN();
@@ -1209,11 +1236,11 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (8 warps, both CTAs)
     // Warp w reads TMEM lanes [32 (w & 3), +32) (the only ones it may touch) and, of the tile's
-    // 256 columns, the half (w - 2) / 4, as eight 16-column chunks.  Thread = row.  The axpy
-    // operand of the whole half-row (256 bytes) is requested before the wait for the accumulator.
+    // 256 columns, the half (w - 4) / 4.  Thread = row.  The axpy operand of the whole half-row
+    // (256 bytes) is requested before the wait for the accumulator.
     const int q = warp & 3;
     const int r = q * 32 + lane;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     PROF_BEGIN();
     for (uint32_t n = 0;; ++n) {
       PROF_LAP(0);
@@ -1233,13 +1260,21 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       const uint32_t aph = (n >> 1) & 1;
       const int cur = ti.k & 1;
       const int ld = mode == 2 ? p.N : p.M;                                   // row pitch of C and D
-      const uint16_t *dbase = mode == 1 ? p.A : p.XY[cur];                    // axpy operand (modes 1, 2)
+      const uint16_t *dbase = p.A;                                            // axpy operand (poly phase)
       uint16_t *cbase = mode == 0 ? p.A : (mode == 1 ? p.B : p.XY[cur ^ 1]);
       const size_t row_off = ((size_t)ti.e * p.M + (size_t)i * BM + r) * ld + (size_t)j * 128 + (size_t)half * 128;
       const uint16_t *drow = dbase + row_off;
       uint16_t *crow = cbase + row_off;
-      uint32_t d[64];                     // the half-row of the axpy operand: 128 bf16
-      if (mode != 0 && active) {
+      uint32_t d[64];                     // the half-row of the axpy operand (poly phase): 128 bf16
+#ifdef ANC_CHAIN_PROFILE
+      if (mode == 1 && active && (g_chain_dbg & 32)) {   // timing experiment: line-granular operand loads
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          ld_gpu_256(drow + ((long)((s & 3) - (lane & 3))) * (long)ld + ((s >> 2) * 4 + (lane & 3)) * 16,
+                     reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
+      } else
+#endif
+      if (mode == 1 && active && DBG_ON(4)) {
 #pragma unroll
         for (int s = 0; s < 8; ++s) ld_gpu_256(drow + s * 16, reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
       }
@@ -1257,57 +1292,80 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         const bool scaled = p.mscale != nullptr && ti.k == 0 && mode != 1;
         const float sc = scaled ? p.mscale[ti.e] : 1.f;
         const float sc2 = __fmul_rn(sc, sc);
-        const float alpha = mode == 0 ? 0.f : (mode == 1 ? p.coef[3 * ti.k + 1] : p.coef[3 * ti.k]);
-        const float beta = mode == 1 ? p.coef[3 * ti.k + 2] : 1.f;
-        const float al = scaled ? __fmul_rn(alpha, sc) : alpha;
-        const float be = scaled ? __fmul_rn(beta, sc) : beta;
+        // poly: B' = b*A + c*(A A) + a*I; apply: X' = B' X (times the Frobenius factor in iteration 0)
+        const float al = mode == 1 ? p.coef[3 * ti.k + 1] : 0.f;
+        const float be = mode == 1 ? p.coef[3 * ti.k + 2] : sc;
+        const float a_diag = p.coef[3 * ti.k];
+        // the matrix's diagonal crosses this warp's 128 columns in the diagonal 128-block only,
+        // at column r of the block
+        const int dcol = (mode == 1 && i == j + half) ? r : -1;
         const bool mirror = mode != 2 && j + half < i;   // block (i, j + half) also lands, transposed, at (j + half, i)
         uint16_t *mcol0 = cbase + ((size_t)ti.e * p.M + (size_t)(j + half) * 128) * p.M + (size_t)i * BM + r;
-        uint32_t va[16], vb[16];
-        tc_ld16(taddr0, va);
+        uint32_t v[64];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          uint32_t(&v)[16] = (s & 1) ? vb : va;
-          uint32_t(&vnext)[16] = (s & 1) ? va : vb;
-          tc_wait_ld();                                       // chunk s has landed
-          if (s < 7) tc_ld16(taddr0 + (s + 1) * 16, vnext);    // chunk s + 1 loads while s is processed
-          uint32_t h[8];
-          if (mode == 0) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const float lo = __uint_as_float(v[2 * k]), hi = __uint_as_float(v[2 * k + 1]);
-              h[k] = scaled ? pack_bf16(__fmul_rn(sc2, lo), __fmul_rn(sc2, hi)) : pack_bf16(lo, hi);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t dw = d[s * 8 + k];
-              const float dlo = __uint_as_float(dw << 16);
-              const float dhi = __uint_as_float(dw & 0xFFFF0000u);
-              h[k] = pack_bf16(__fmaf_rn(be, __uint_as_float(v[2 * k]), __fmul_rn(al, dlo)),
-                               __fmaf_rn(be, __uint_as_float(v[2 * k + 1]), __fmul_rn(al, dhi)));
-            }
+        for (int hh = 0; hh < 2; ++hh) {                      // two round trips of 64 columns
+          if (DBG_ON(8)) {
+            tc_ld64(taddr0 + hh * 64, v);
+            tc_wait_ld();
           }
-          st_256(crow + s * 16, h);
-          if (mirror) {
-            uint16_t *mcol = mcol0 + (size_t)(s * 16) * p.M;
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-              mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const int s = hh * 4 + s4;
+            uint32_t h[8];
+            if (mode == 0) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const float lo = __uint_as_float(v[s4 * 16 + 2 * k]), hi = __uint_as_float(v[s4 * 16 + 2 * k + 1]);
+                h[k] = scaled ? pack_bf16(__fmul_rn(sc2, lo), __fmul_rn(sc2, hi)) : pack_bf16(lo, hi);
+              }
+            } else if (mode == 2) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                h[k] = pack_bf16(__fmul_rn(be, __uint_as_float(v[s4 * 16 + 2 * k])),
+                                 __fmul_rn(be, __uint_as_float(v[s4 * 16 + 2 * k + 1])));
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t dw = d[s * 8 + k];
+                const float dlo = __uint_as_float(dw << 16);
+                const float dhi = __uint_as_float(dw & 0xFFFF0000u);
+                float lo = __fmaf_rn(be, __uint_as_float(v[s4 * 16 + 2 * k]), __fmul_rn(al, dlo));
+                float hi = __fmaf_rn(be, __uint_as_float(v[s4 * 16 + 2 * k + 1]), __fmul_rn(al, dhi));
+                if (dcol == s * 16 + 2 * k) lo = __fadd_rn(lo, a_diag);
+                if (dcol == s * 16 + 2 * k + 1) hi = __fadd_rn(hi, a_diag);
+                h[k] = pack_bf16(lo, hi);
+              }
+            }
+#ifdef ANC_CHAIN_PROFILE
+            if (g_chain_dbg & 16) {   // timing experiment: line-granular addressing (wrong placement, same bytes)
+              uint16_t *alt = crow + ((long)((s & 3) - (lane & 3))) * (long)ld + ((s >> 2) * 4 + (lane & 3)) * 16;
+              st_256(alt, h);
+            } else
+#endif
+            if (DBG_ON(1)) st_256(crow + s * 16, h);
+            if (mirror && DBG_ON(2)) {
+              uint16_t *mcol = mcol0 + (size_t)(s * 16) * p.M;
+#pragma unroll
+              for (int k = 0; k < 16; ++k)
+                mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
+            }
           }
         }
       }
+      PROF_LAP(4);                  // TMEM -> registers -> global (+ mirrored stores)
       // accumulator read: hand the TMEM buffer back; then pass this warp's part of the tile to the
       // signalling thread (the barrier orders the stores of all lanes before its release)
       tc_fence_before();
       __syncwarp();
+      PROF_LAP(5);                  // fence + warp barrier
       if (lane == 0) {
         mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        PROF_LAP(6);                // handing the accumulator back (arrival on the leader's barrier)
         mbar_arrive(done_bar(slot));
+        PROF_LAP(7);                // passing the tile to the signalling thread
       }
-      PROF_LAP(5);                  // TMEM -> registers -> global (+ mirrored stores)
     }
-    if (threadIdx.x == 64) PROF_END(2);
+    if (threadIdx.x == 128) PROF_END(2);
   }
 
   tc_fence_before();
@@ -1433,7 +1491,7 @@ void anc_gemm_cache_destroy(anc_ctx *ctx) {
 }
 
 int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t *Q, uint16_t *C,
-                       int E, int M, int N, float alpha, float beta, const float *mscale,
+                       int E, int M, int N, float alpha, float beta, float diag, const float *mscale,
                        cudaStream_t st) {
   ANC_REQUIRE(mode >= 0 && mode <= 2, "bad mode %d", mode);
   ANC_REQUIRE(E > 0 && M > 0 && N > 0 && M % 128 == 0 && N % 128 == 0,
@@ -1485,6 +1543,8 @@ int anc_launch_ns_gemm(anc_ctx *ctx, int mode, const uint16_t *P, const uint16_t
   p.mode = mode;
   p.alpha = alpha;
   p.beta = beta;
+  p.diag = mode == 1 ? diag : 0.f;
+  p.use_d = (mode == 1 || (mode == 2 && alpha != 0.f)) ? 1 : 0;
   if (pair) {
     if (!gc->attr2_set) {
       ANC_CUDA(cudaFuncSetAttribute(ns_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1616,7 +1676,7 @@ extern "C" int anc_ns_gemm_phase(anc_ctx *ctx, int mode, const uint16_t *P, cons
                                  void *stream) {
   ANC_REQUIRE(ctx && P && C, "NULL argument");
   anc_device_guard guard(ctx->device);
-  return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, nullptr,
+  return anc_launch_ns_gemm(ctx, mode, P, Q, C, E, M, N, alpha, beta, 0.f, nullptr,
                             anc_pick_stream(ctx, stream));
 }
 
@@ -1652,6 +1712,10 @@ extern "C" int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit) {
 #ifdef ANC_CHAIN_PROFILE
 // Reads (and clears) the stall counters: rows of 8 counters for (CTA, role), roles 0 producer,
 // 1 MMA issuer, 2 epilogue (its elected thread), 3 store thread, 4 scheduler.
+extern "C" __attribute__((visibility("default"))) int anc_debug_chain_flags(int flags) {
+  ANC_CUDA(cudaMemcpyToSymbol(g_chain_dbg, &flags, sizeof(flags)));
+  return ANC_OK;
+}
 extern "C" __attribute__((visibility("default"))) int anc_debug_chain_prof(unsigned long long *out, int n_ctas) {
   const size_t bytes = (size_t)n_ctas * 5 * 8 * sizeof(unsigned long long);
   ANC_CUDA(cudaDeviceSynchronize());

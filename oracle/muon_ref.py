@@ -70,9 +70,10 @@ def fro_recip(Xf32, eps=1e-7):
 
 def ns_bf16_chain(X16, steps=5, schedule=None, eps=1e-7, recip=None):
     """Emulates the device chain on a (M,N) bf16-bit matrix with M <= N: every stored
-    matrix (scaled X, A, B, Y) is rounded to bf16; products accumulate in higher
-    precision and the axpy combines happen before the rounding (fused epilogues).
-    Tolerance-level model of the device result, used for error budgeting only."""
+    matrix (scaled X, A, B', Y) is rounded to bf16; products accumulate in higher
+    precision and the combines happen before the rounding (fused epilogues).  As on the
+    device, the a*X term rides in the polynomial's diagonal: B' = b A + c A A + a I and
+    X' = B' X.  Tolerance-level model of the device result, used for error budgeting only."""
     X = bits_f32(X16).astype(np.float32)
     if recip is None:
         recip = fro_recip(X, eps)
@@ -80,8 +81,9 @@ def ns_bf16_chain(X16, steps=5, schedule=None, eps=1e-7, recip=None):
     for k in range(steps):
         a, b, c = (np.float32(t) for t in coef_at(schedule, k))
         A = rne_f32(X @ X.T)
-        B = rne_f32(b * A + c * (A @ A))
-        X = rne_f32(a * X + B @ X)
+        B = b * A + c * (A @ A)
+        B[np.diag_indices_from(B)] += a
+        X = rne_f32(rne_f32(B) @ X)
     return rne_bits(X)
 
 
