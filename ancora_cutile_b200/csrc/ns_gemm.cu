@@ -42,7 +42,7 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 19;   // tries; each may suspend up to ~2 us: about a second
 
 struct GemmParams {
   const uint16_t *D;      // axpy operand (modes 1, 2), same layout as C
@@ -71,14 +71,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// The last operand is the time (ns) the hardware may keep the thread suspended inside the
+// instruction: a suspended thread uses no issue slots, unlike a loop around a test.
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
@@ -775,12 +777,12 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // The tile -> output mapping and each tile's K order are those of the per-phase kernel, so
 // the results are bitwise the same.
 //
-// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA), warp 2 scheduler
-// (leader CTA): it claims a tile, waits for the tile's dependencies, decodes it and publishes
-// it to both CTAs through a small ring in shared memory; warp 3 raises the matrix's completion
-// counter once the epilogue warps have stored their part of a tile (a release at GPU scope
-// waits for the stores to be performed, which would otherwise stall the epilogue for a
-// microsecond per tile); warps 4-11 epilogue.
+// Roles (384 threads): warps 0-7 epilogue; then four single-thread roles: TMA producer, MMA
+// issuer (leader CTA), scheduler (leader CTA): it claims a tile, waits for the tile's
+// dependencies, decodes it and publishes it to both CTAs through a small ring in shared
+// memory; and a thread that raises the matrix's completion counter once the epilogue warps
+// have stored their part of a tile (a release at GPU scope waits for the stores to be
+// performed, which would otherwise stall the epilogue for a microsecond per tile).
 //
 // Shared memory holds nothing but the operand ring (7 stages of 32 KiB).  With 256x256 pair
 // tiles the tensor cores read 64 B/clk of operands from shared memory and TMA writes another
@@ -797,6 +799,10 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // roles drain and return.
 // ====================================================================================
 constexpr int kChainThreads = 384;
+// Warps 0-7 are the epilogue, 8-11 the four single-thread roles.  The roles spend most of their
+// time polling barriers; as the lowest-numbered warps of their scheduler partitions they kept the
+// issue slots from the epilogue warps (a 64-column combine took 2.7 kclk instead of a few hundred).
+constexpr int kProducerWarp = 8, kMmaWarp = 9, kSchedWarp = 10, kSignalWarp = 11;
 constexpr int kSchedSlots = 4;
 constexpr int kMaxChainSteps = 16;
 constexpr int kStages3 = 7;
@@ -873,10 +879,10 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) 
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
@@ -1007,7 +1013,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(kTmemCols)
@@ -1053,7 +1059,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
     return ti;
   };
 
-  if (warp == 2) {
+  if (warp == kSchedWarp) {
     // ------------------------------------------------------------ scheduler (leader only)
     if (lane == 0 && crank == 0) {
       const uint32_t limit = p.spin_limit;
@@ -1107,7 +1113,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       }
       PROF_END(4);
     }
-  } else if (warp == 0) {
+  } else if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
@@ -1153,7 +1159,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       }
       PROF_END(0);
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && crank == 0) {
       uint32_t it = 0;
@@ -1204,7 +1210,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       }
       PROF_END(1);
     }
-  } else if (warp == 3) {
+  } else if (warp == kSignalWarp) {
     // ------------------------------------------------------------ completion signal (both CTAs)
     if (lane == 0) {
       PROF_BEGIN();
@@ -1236,16 +1242,15 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (8 warps, both CTAs)
     // Warp w reads TMEM lanes [32 (w & 3), +32) (the only ones it may touch) and, of the tile's
-    // 256 columns, the half (w - 4) / 4.  Thread = row.  The axpy operand of the whole half-row
+    // 256 columns, the half w / 4.  Thread = row.  The axpy operand of the whole half-row
     // (256 bytes) is requested before the wait for the accumulator.
     const int q = warp & 3;
     const int r = q * 32 + lane;
-    const int half = (warp - 4) >> 2;
+    const int half = warp >> 2;
     PROF_BEGIN();
     for (uint32_t n = 0;; ++n) {
-      PROF_LAP(0);
       const ChainTile ti = ring_get(n, false, ANC_DEV_TIMEOUT_EPI);
-      PROF_LAP(1);                  // waiting for a tile
+      PROF_LAP(0);                  // waiting for a tile (+ loop overhead)
       // warp-uniform end of the role (a lane that gave up on the wait must take its warp along:
       // the TMEM loads below are warp-wide)
       if (__any_sync(0xFFFFFFFFu, ti.t == kTileDone)) break;
@@ -1278,15 +1283,16 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
 #pragma unroll
         for (int s = 0; s < 8; ++s) ld_gpu_256(drow + s * 16, reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
       }
-      PROF_LAP(2);                  // issuing the axpy operand loads
+      PROF_LAP(1);                  // issuing the axpy operand loads
       bool ok = mbar_wait(tfull_bar(buf), aph, abort_flag);
-      PROF_LAP(3);                  // waiting for the accumulator (MMA-bound when large)
+      PROF_LAP(2);                  // waiting for the accumulator (MMA-bound when large)
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) {
         if (lane == 0 && !*abort_flag) raise_abort(ANC_DEV_TIMEOUT_EPI);
         break;
       }
       tc_fence_after();
+      PROF_LAP(3);                  // warp vote + fence
       if (active) {
         const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u + (uint32_t)half * 128u;
         const bool scaled = p.mscale != nullptr && ti.k == 0 && mode != 1;
@@ -1308,6 +1314,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
             tc_ld64(taddr0 + hh * 64, v);
             tc_wait_ld();
           }
+          if (hh == 0) PROF_LAP(4); else PROF_LAP(6);   // TMEM round trips
 #pragma unroll
           for (int s4 = 0; s4 < 4; ++s4) {
             const int s = hh * 4 + s4;
@@ -1350,29 +1357,27 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
                 mcol[(size_t)k * p.M] = (uint16_t)((k & 1) ? (h[k >> 1] >> 16) : (h[k >> 1] & 0xFFFFu));
             }
           }
+          if (hh == 0) PROF_LAP(5);   // combine + stores of the first 64 columns
         }
       }
-      PROF_LAP(4);                  // TMEM -> registers -> global (+ mirrored stores)
+      PROF_LAP(7);                  // combine + stores of the last 64 columns
       // accumulator read: hand the TMEM buffer back; then pass this warp's part of the tile to the
       // signalling thread (the barrier orders the stores of all lanes before its release)
       tc_fence_before();
       __syncwarp();
-      PROF_LAP(5);                  // fence + warp barrier
       if (lane == 0) {
         mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
-        PROF_LAP(6);                // handing the accumulator back (arrival on the leader's barrier)
         mbar_arrive(done_bar(slot));
-        PROF_LAP(7);                // passing the tile to the signalling thread
       }
     }
-    if (threadIdx.x == 128) PROF_END(2);
+    if (threadIdx.x == 0) PROF_END(2);
   }
 
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();
   tc_fence_after();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(kTmemCols)
                  : "memory");
