@@ -52,6 +52,7 @@ SIGNATURES = {
     "anc_device_count": (_i, [C.POINTER(_i)]),
     "anc_ctx_create": (_i, [_i, _vp, _pp]),
     "anc_ctx_destroy": (_i, [_vp]),
+    "anc_ctx_reserve_sms": (_i, [_vp, _i]),
     "anc_ctx_stream": (_i, [_vp, _pp]),
     "anc_ctx_sync": (_i, [_vp, _vp]),
     "anc_ctx_status": (_i, [_vp, C.POINTER(C.c_uint32)]),

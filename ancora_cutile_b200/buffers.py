@@ -41,6 +41,10 @@ class Context:
         L.check(L.lib().anc_ctx_stream(self.handle, C.byref(s)))
         self.stream = s.value or 0
 
+    def reserve_sms(self, n):
+        """SMs the persistent Newton-Schulz kernel leaves free for other streams' kernels."""
+        L.check(L.lib().anc_ctx_reserve_sms(self.handle, int(n)))
+
     def sync(self, stream=None):
         L.check(L.lib().anc_ctx_sync(self.handle, C.c_void_p(stream or None)))
 

@@ -17,6 +17,7 @@ struct anc_ctx {
   void *d_flush;            // L2 flush buffer, allocated on first use
   size_t flush_bytes;
   int sm_count;
+  int reserved_sms;         // SMs the persistent Newton-Schulz kernel leaves to other streams
 };
 
 // entries of the device tables the Muon plan builds for the group launches

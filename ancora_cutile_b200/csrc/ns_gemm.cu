@@ -1656,7 +1656,12 @@ int anc_launch_ns_chain(anc_ctx *ctx, uint16_t *X, uint16_t *Y, uint16_t *A, uin
   p.total_tiles = (uint32_t)total;
   p.spin_limit = spin_limit ? spin_limit : kSpinLimit;
   for (int i = 0; i < 3 * steps; ++i) p.coef[i] = coeffs[i];
-  uint64_t pairs = (uint64_t)(ctx->sm_count / 2);
+  // SMs left free for kernels of other streams (a collective that overlaps the chain): the chain
+  // CTAs are persistent and fill an SM each, so a kernel that arrives after them would otherwise
+  // wait for the whole chain.  Set per context (anc_ctx_reserve_sms); 0 by default.
+  int usable = ctx->sm_count - ctx->reserved_sms;
+  if (usable < 2) usable = 2;
+  uint64_t pairs = (uint64_t)(usable / 2);
   if (total < pairs) pairs = total;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));

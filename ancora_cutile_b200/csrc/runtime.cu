@@ -94,6 +94,13 @@ int anc_ctx_destroy(anc_ctx *ctx) {
   return ANC_OK;
 }
 
+int anc_ctx_reserve_sms(anc_ctx *ctx, int n_sms) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  ANC_REQUIRE(n_sms >= 0 && n_sms <= ctx->sm_count - 2, "cannot reserve %d of %d SMs", n_sms, ctx->sm_count);
+  ctx->reserved_sms = n_sms;
+  return ANC_OK;
+}
+
 int anc_ctx_stream(anc_ctx *ctx, void **stream) {
   ANC_REQUIRE(ctx && stream, "NULL argument");
   *stream = (void *)ctx->stream;

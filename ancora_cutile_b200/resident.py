@@ -527,13 +527,20 @@ class ResidentHybrid:
             L.check(lib.anc_stream_wait_event(cs, start.handle))
         h2d = d2h = 0
         gi = 0
+        gspans = []
         for op, what in sched:
             if op == "gather":
                 ev = ev_g[gi]
                 gi += 1
                 ev.record(si)
                 L.check(lib.anc_stream_wait_event(cs, ev.handle))
+                if trace is not None:              # when each all-gather ran, on the device clock
+                    g0, g1 = Event(), Event()
+                    g0.record(cs)
                 self._gather_group(what, cs)
+                if trace is not None:
+                    g1.record(cs)
+                    gspans.append((str(what), g0, g1))
                 continue
             k, u = what, units[what]
             h2d += self._h2d_unit(u, s_in)
@@ -563,7 +570,11 @@ class ResidentHybrid:
                          d2h_done_ms=start.elapsed_ms(m_out),
                          exchange_done_ms=start.elapsed_ms(m_x) if cs is not None else None,
                          total_ms=start.elapsed_ms(end), units=nu,
+                         gathers=[[w, start.elapsed_ms(a), start.elapsed_ms(b)] for w, a, b in gspans],
                          host_stage_ms=(t_staged - t_host0) * 1e3, host_enqueue_ms=(t_enq - t_staged) * 1e3)
+        for _, a, b in gspans:
+            a.destroy()
+            b.destroy()
         return self._weight_views(), h2d, d2h
 
     def download_weights_bits(self, si=None, sync=True):

@@ -330,6 +330,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    if world > 1 and os.environ.get("ANCORA_RESERVE_SMS"):
+        ctx.reserve_sms(int(os.environ["ANCORA_RESERVE_SMS"]))
+        config["reserved_sms"] = int(os.environ["ANCORA_RESERVE_SMS"])
     anc.set_polar_express(True)
     params = S.synthetic_params(shp, seed=0)
     no_decay = tuple(n for n, s in shp.items() if len(s) == 1)
@@ -485,8 +488,10 @@ def main():
         e2e_ms = max_over_ranks(max(e0.elapsed_ms(e1) / args.steps, wall_ms))
         # where one step's time goes on this rank (device clock, ms from the start of the call, mean over
         # the timed steps): the copies run on their own streams beside the compute stream
-        keys = [k for k in traces[0] if traces[0][k] is not None]
+        keys = [k for k in traces[0] if traces[0][k] is not None and k != "gathers"]
         brk = {k: float(np.mean([t[k] for t in traces])) for k in keys}
+        if traces[-1].get("gathers"):
+            brk["gathers_last_step"] = traces[-1]["gathers"]      # [group, start ms, end ms] of each all-gather
         brk["pcie_gbs_each_way"] = h2d / (max(brk["h2d_done_ms"], brk["d2h_done_ms"]) * 1e-3) / 1e9
         out["e2e"] = {"value": total_params / (e2e_ms * 1e-3), "unit": "params/s", "ms_per_step": e2e_ms,
                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "breakdown": brk,

@@ -65,6 +65,10 @@ ANC_API int anc_device_count(int *count);
  * create_stream(): tests/optim/test_adamw.py:15-17).  stream==NULL creates one. */
 ANC_API int anc_ctx_create(int device, void *stream, anc_ctx **out);
 ANC_API int anc_ctx_destroy(anc_ctx *ctx);
+/* The persistent Newton-Schulz kernel fills every SM it is given for the length of a whole chain.
+ * Reserving n SMs keeps it off them, so that a kernel of another stream (the NCCL all-gather that
+ * overlaps the step) finds room at once.  0 by default; no counterpart in the reference. */
+ANC_API int anc_ctx_reserve_sms(anc_ctx *ctx, int n_sms);
 ANC_API int anc_ctx_stream(anc_ctx *ctx, void **stream);
 ANC_API int anc_ctx_sync(anc_ctx *ctx, void *stream);
 /* Reads and clears the device status word (0 = no kernel reported a problem). */

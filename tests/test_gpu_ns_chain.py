@@ -155,6 +155,23 @@ def test_single_launch_chain_equals_one_launch_per_phase(ctx, monkeypatch, E, M,
         assert np.array_equal(dev_ns(ctx, Xb, E, M, N, steps, muon_ns.PE_SCHEDULE), chain)
 
 
+def test_reserved_sms_do_not_change_the_bits(ctx):
+    """Leaving SMs to other streams (what a rank does while NCCL's all-gather overlaps the chain)
+    changes how many CTA pairs share the tile queue, not what a tile computes."""
+    rng = np.random.default_rng(11)
+    E, M, N = 9, 512, 1024
+    Xb = f32_to_bf16_bits((rng.standard_normal((E * M, N)) * 1e-3).astype(np.float32))
+    want = dev_ns(ctx, Xb, E, M, N, 5, muon_ns.PE_SCHEDULE)
+    try:
+        for n in (16, 100, 146):
+            ctx.reserve_sms(n)
+            assert np.array_equal(dev_ns(ctx, Xb, E, M, N, 5, muon_ns.PE_SCHEDULE), want), n
+    finally:
+        ctx.reserve_sms(0)
+    with pytest.raises(anc.AncoraError):
+        ctx.reserve_sms(10 ** 6)
+
+
 def test_dependency_wait_runs_out_and_context_survives(ctx):
     """A tile whose dependency nobody completes: the bounded wait gives up, status bit 0x10 is
     set, the kernel drains and returns, and the context keeps working (no trap, no hang)."""
