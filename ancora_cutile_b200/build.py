@@ -2,6 +2,8 @@
 
     python -m ancora_cutile_b200.build          # incremental
     python -m ancora_cutile_b200.build --force
+    python -m ancora_cutile_b200.build --profile   # libancora_b200_prof.so: stall accounting compiled
+                                                   # into the Newton-Schulz chain kernel (profile_chain.py)
 
 nvcc cross-compiles without a GPU.  The library links the static CUDA runtime only;
 the driver's tensor-map encoder and NCCL are looked up at run time, so the shared
@@ -37,8 +39,23 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+PROF_LIB = os.path.join(PKG, "libancora_b200_prof.so")
+
+
+def build(force=False, verbose=False, profile=False):
     nvcc = _nvcc()
+    global OBJ, LIB
+    if profile:
+        saved = OBJ, LIB
+        OBJ, LIB = os.path.join(PKG, "build_prof"), PROF_LIB
+        try:
+            return _build(nvcc, force, verbose, ["-DANC_CHAIN_PROFILE"])
+        finally:
+            OBJ, LIB = saved
+    return _build(nvcc, force, verbose, [])
+
+
+def _build(nvcc, force, verbose, extra):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, "anc_internal.h"),
                os.path.join(PKG, "..", "include", "ancora_b200.h")]
@@ -49,7 +66,7 @@ def build(force=False, verbose=False):
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            jobs.append([nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o])
+            jobs.append([nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o])
 
     def run(cmd):
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -68,4 +85,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, profile="--profile" in sys.argv))

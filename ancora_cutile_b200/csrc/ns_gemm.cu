@@ -944,10 +944,6 @@ __device__ __forceinline__ void st_256(void *ptr, const uint32_t *r) {
 // Optional per-role stall accounting (compiled in with -DANC_CHAIN_PROFILE only): every role adds
 // the cycles it spent in each of its waits to a per-CTA row of a device array.
 #ifdef ANC_CHAIN_PROFILE
-// timing experiments (profile build only; results are wrong when set): 1 skip the result stores,
-// 2 skip the mirrored stores, 4 skip the axpy operand loads, 8 skip the TMEM loads
-__device__ int g_chain_dbg = 0;
-#define DBG_ON(bit) ((g_chain_dbg & (bit)) == 0)
 __device__ unsigned long long g_chain_prof[512 * 5 * 8];
 #define PROF_BEGIN() unsigned long long _pt = clock64(); unsigned long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_LAP(k)                      \
@@ -962,7 +958,6 @@ __device__ unsigned long long g_chain_prof[512 * 5 * 8];
       atomicAdd(&g_chain_prof[((blockIdx.x % 512) * 5 + (role)) * 8 + _k], _pa[_k]);        \
   } while (0)
 #else
-#define DBG_ON(bit) true
 #define PROF_BEGIN() do { } while (0)
 #define PROF_LAP(k) do { } while (0)
 #define PROF_END(role) do { } while (0)
@@ -1271,15 +1266,7 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
       const uint16_t *drow = dbase + row_off;
       uint16_t *crow = cbase + row_off;
       uint32_t d[64];                     // the half-row of the axpy operand (poly phase): 128 bf16
-#ifdef ANC_CHAIN_PROFILE
-      if (mode == 1 && active && (g_chain_dbg & 32)) {   // timing experiment: line-granular operand loads
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          ld_gpu_256(drow + ((long)((s & 3) - (lane & 3))) * (long)ld + ((s >> 2) * 4 + (lane & 3)) * 16,
-                     reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
-      } else
-#endif
-      if (mode == 1 && active && DBG_ON(4)) {
+      if (mode == 1 && active) {
 #pragma unroll
         for (int s = 0; s < 8; ++s) ld_gpu_256(drow + s * 16, reinterpret_cast<uint32_t(&)[8]>(d[s * 8]));
       }
@@ -1310,10 +1297,8 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
         uint32_t v[64];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {                      // two round trips of 64 columns
-          if (DBG_ON(8)) {
-            tc_ld64(taddr0 + hh * 64, v);
-            tc_wait_ld();
-          }
+          tc_ld64(taddr0 + hh * 64, v);
+          tc_wait_ld();
           if (hh == 0) PROF_LAP(4); else PROF_LAP(6);   // TMEM round trips
 #pragma unroll
           for (int s4 = 0; s4 < 4; ++s4) {
@@ -1343,14 +1328,8 @@ ns_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ 
                 h[k] = pack_bf16(lo, hi);
               }
             }
-#ifdef ANC_CHAIN_PROFILE
-            if (g_chain_dbg & 16) {   // timing experiment: line-granular addressing (wrong placement, same bytes)
-              uint16_t *alt = crow + ((long)((s & 3) - (lane & 3))) * (long)ld + ((s >> 2) * 4 + (lane & 3)) * 16;
-              st_256(alt, h);
-            } else
-#endif
-            if (DBG_ON(1)) st_256(crow + s * 16, h);
-            if (mirror && DBG_ON(2)) {
+            st_256(crow + s * 16, h);
+            if (mirror) {
               uint16_t *mcol = mcol0 + (size_t)(s * 16) * p.M;
 #pragma unroll
               for (int k = 0; k < 16; ++k)
@@ -1722,10 +1701,6 @@ extern "C" int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit) {
 #ifdef ANC_CHAIN_PROFILE
 // Reads (and clears) the stall counters: rows of 8 counters for (CTA, role), roles 0 producer,
 // 1 MMA issuer, 2 epilogue (its elected thread), 3 store thread, 4 scheduler.
-extern "C" __attribute__((visibility("default"))) int anc_debug_chain_flags(int flags) {
-  ANC_CUDA(cudaMemcpyToSymbol(g_chain_dbg, &flags, sizeof(flags)));
-  return ANC_OK;
-}
 extern "C" __attribute__((visibility("default"))) int anc_debug_chain_prof(unsigned long long *out, int n_ctas) {
   const size_t bytes = (size_t)n_ctas * 5 * 8 * sizeof(unsigned long long);
   ANC_CUDA(cudaDeviceSynchronize());
