@@ -284,7 +284,7 @@ class Muon:
         if self._plan is None:
             return
         for n, s in self.st.items():
-            s["G"].upload(self._grad_host(grads[n]), si, sync=True)
+            s["G"].upload(self._grad_host(grads[n]), si, sync=False)     # one sync at the end of the step
         self._plan.step(si, self.lr, self.mom, self.nesterov, self.ns, _schedule(self._sched))
         self.ctx.sync(si)
         self.ctx.check_status()
