@@ -5,6 +5,8 @@
 #endif
 #include <sched.h>
 #include <stdlib.h>
+#include <sys/syscall.h>
+#include <unistd.h>
 #include <string.h>
 #include "anc_internal.h"
 
@@ -218,17 +220,30 @@ static bool parse_cpulist(const char *s, cpu_set_t *set) {
 int anc_host_alloc_near(int device, size_t bytes, void **hptr) {
   ANC_REQUIRE(hptr, "hptr is NULL");
   *hptr = nullptr;
-  // Page-locked memory lands on the NUMA node of the thread that allocates it.  Bind this thread
-  // to the CPUs next to the GPU for the duration of the allocation, so that host<->device copies
-  // do not cross the socket interconnect; any failure on the way falls back to a plain allocation.
+  // Page-locked memory lands where the allocating thread's memory policy and CPU put it.  For the
+  // duration of the allocation this thread prefers the GPU's NUMA node (set_mempolicy; works even
+  // when the process may not run on that node's CPUs) and, where allowed, runs on the CPUs next
+  // to the GPU, so that host<->device copies do not cross the socket interconnect.  Any failure on
+  // the way falls back to a plain allocation.
   cpu_set_t saved, local;
-  bool bound = false;
+  bool bound = false, policy = false;
   char busid[32] = {0};
   if (sched_getaffinity(0, sizeof(saved), &saved) == 0 &&
       cudaDeviceGetPCIBusId(busid, (int)sizeof(busid), device) == cudaSuccess) {
     for (char *c = busid; *c; ++c)
       if (*c >= 'A' && *c <= 'F') *c = (char)(*c - 'A' + 'a');
     char path[128];
+    snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/numa_node", busid);
+    FILE *fn = fopen(path, "r");
+    if (fn) {
+      int node = -1;
+      if (fscanf(fn, "%d", &node) == 1 && node >= 0 && node < 1024) {
+        unsigned long mask[16] = {0};
+        mask[node / (8 * sizeof(unsigned long))] |= 1ul << (node % (8 * sizeof(unsigned long)));
+        policy = syscall(SYS_set_mempolicy, 1 /* MPOL_PREFERRED */, mask, 1024ul) == 0;
+      }
+      fclose(fn);
+    }
     snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/local_cpulist", busid);
     FILE *f = fopen(path, "r");
     if (f) {
@@ -244,8 +259,9 @@ int anc_host_alloc_near(int device, size_t bytes, void **hptr) {
     cudaGetLastError();
   }
   int rc = anc_host_alloc(bytes, hptr);
-  if (rc == ANC_OK && bound && bytes) memset(*hptr, 0, bytes);   // touch while bound
+  if (rc == ANC_OK && (bound || policy) && bytes) memset(*hptr, 0, bytes);   // touch while the placement holds
   if (bound) sched_setaffinity(0, sizeof(saved), &saved);
+  if (policy) syscall(SYS_set_mempolicy, 0 /* MPOL_DEFAULT */, (unsigned long *)nullptr, 0ul);
   return rc;
 }
 
