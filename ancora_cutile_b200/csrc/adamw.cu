@@ -16,10 +16,11 @@
 #include <vector>
 #include "anc_internal.h"
 #include "philox.cuh"
+#include "stream_ring.cuh"
 
 namespace {
 
-struct TensorEntry {   // 64 bytes, device resident
+struct TensorEntry {   // host side only
   const void *g;
   float *p;
   float *m;
@@ -31,14 +32,34 @@ struct TensorEntry {   // 64 bytes, device resident
   uint32_t vec_ok;      // all five pointers 16-byte aligned
 };
 
-struct Chunk {          // 16 bytes
-  uint64_t start;       // first element inside the tensor (multiple of 8)
-  uint32_t tensor;
+// One stage of work: at most kChunkElems consecutive elements of one tensor.  Self-contained
+// (the pointers are those of the chunk's first element) so that the thread that feeds the
+// ring needs one table read per stage, issued a stage ahead.
+struct Chunk {          // 64 bytes, device resident
+  const void *g;
+  float *p;
+  float *m;
+  float *v;
+  uint16_t *p16;
+  uint64_t gidx;        // arena index of the first element (a multiple of 8): the Philox position
   uint32_t count;
+  float wd;
+  uint32_t aligned;     // the five addresses are 16-byte aligned
+  uint32_t bulk;        // aligned and count a multiple of 8: the stage is filled by bulk copies
 };
+static_assert(sizeof(Chunk) == 64, "chunk record");
 
-constexpr int kThreads = 256;
-constexpr int kChunkElems = 8192;   // 4 passes of 256 threads x 8 elements
+constexpr int kThreads = 256;       // computing threads; one more warp feeds the ring
+constexpr int kChunkElems = 2048;   // 256 threads x 8 elements
+constexpr int kHdrBytes = 128;      // the chunk record travels with its stage
+
+template <bool kGradF32>
+struct Ring {
+  static constexpr int kStages = kGradF32 ? 6 : 7;
+  static constexpr uint32_t kGradBytes = kGradF32 ? 4u : 2u;
+  static constexpr uint32_t kStageBytes = kHdrBytes + kChunkElems * (12u + kGradBytes);
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes;   // 201,600 / 197,376 bytes
+};
 
 struct Scalars {
   float b1, omb1, b2, omb2, eps, lr, ibc1, ibc2;
@@ -74,13 +95,95 @@ __device__ __forceinline__ void load_grad8(const void *g, uint64_t i, float out[
   }
 }
 
+// The update of one 8-element group held in registers and its stores (i = offset inside the chunk).
+template <bool kSR>
+__device__ __forceinline__ void finish8(const Chunk &ch, uint32_t i, float g[8], float p[8], float m[8],
+                                        float v[8], const Scalars &s, uint32_t seed_lo, uint32_t seed_hi,
+                                        uint32_t step_lo, uint32_t step_hi) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) adamw_elem(g[k], p[k], m[k], v[k], ch.wd, s);
+  uint32_t h[8];
+  if constexpr (kSR) {
+    const uint64_t blk = (ch.gidx + i) >> 3;
+    uint32_t w[4];
+    philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), step_lo, step_hi, seed_lo, seed_hi, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      h[2 * k] = bf16_sr(p[2 * k], w[k] & 0xFFFFu);
+      h[2 * k + 1] = bf16_sr(p[2 * k + 1], w[k] >> 16);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) h[k] = bf16_rne(p[k]);
+  }
+  __stcs(reinterpret_cast<float4 *>(ch.p + i), make_float4(p[0], p[1], p[2], p[3]));
+  __stcs(reinterpret_cast<float4 *>(ch.p + i) + 1, make_float4(p[4], p[5], p[6], p[7]));
+  __stcs(reinterpret_cast<float4 *>(ch.m + i), make_float4(m[0], m[1], m[2], m[3]));
+  __stcs(reinterpret_cast<float4 *>(ch.m + i) + 1, make_float4(m[4], m[5], m[6], m[7]));
+  __stcs(reinterpret_cast<float4 *>(ch.v + i), make_float4(v[0], v[1], v[2], v[3]));
+  __stcs(reinterpret_cast<float4 *>(ch.v + i) + 1, make_float4(v[4], v[5], v[6], v[7]));
+  *reinterpret_cast<uint4 *>(ch.p16 + i) =
+      make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+}
+
+// A chunk the bulk copies cannot serve (a tensor whose pointers are not 16-byte aligned, or the
+// ragged last chunk of a tensor): plain loads, 128-bit where the alignment allows, then
+// element by element.  Same arithmetic, same Philox block per 8 elements.
 template <bool kGradF32, bool kSR>
-__global__ void __launch_bounds__(kThreads)
-adamw_multi_kernel(const TensorEntry *__restrict__ tensors, const Chunk *__restrict__ chunks,
-                   uint32_t n_chunks, uint32_t n_tensors, Scalars s, uint32_t seed_lo,
+__device__ __forceinline__ void direct_chunk(const Chunk &ch, const Scalars &s, uint32_t seed_lo,
+                                             uint32_t seed_hi, uint32_t step_lo, uint32_t step_hi) {
+  const uint32_t groups = ch.aligned ? (ch.count >> 3) : 0u;
+  for (uint32_t gi = threadIdx.x; gi < groups; gi += kThreads) {
+    const uint32_t i = gi * 8;
+    float g[8], p[8], m[8], v[8];
+    load_grad8<kGradF32>(ch.g, i, g);
+    const float4 p0 = __ldcs(reinterpret_cast<const float4 *>(ch.p + i));
+    const float4 p1 = __ldcs(reinterpret_cast<const float4 *>(ch.p + i) + 1);
+    const float4 m0 = __ldcs(reinterpret_cast<const float4 *>(ch.m + i));
+    const float4 m1 = __ldcs(reinterpret_cast<const float4 *>(ch.m + i) + 1);
+    const float4 v0 = __ldcs(reinterpret_cast<const float4 *>(ch.v + i));
+    const float4 v1 = __ldcs(reinterpret_cast<const float4 *>(ch.v + i) + 1);
+    p[0] = p0.x; p[1] = p0.y; p[2] = p0.z; p[3] = p0.w; p[4] = p1.x; p[5] = p1.y; p[6] = p1.z; p[7] = p1.w;
+    m[0] = m0.x; m[1] = m0.y; m[2] = m0.z; m[3] = m0.w; m[4] = m1.x; m[5] = m1.y; m[6] = m1.z; m[7] = m1.w;
+    v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+    finish8<kSR>(ch, i, g, p, m, v, s, seed_lo, seed_hi, step_lo, step_hi);
+  }
+  for (uint32_t i = (groups << 3) + threadIdx.x; i < ch.count; i += kThreads) {
+    float g;
+    if constexpr (kGradF32) g = ((const float *)ch.g)[i];
+    else g = __uint_as_float((uint32_t)((const uint16_t *)ch.g)[i] << 16);
+    float p = ch.p[i], m = ch.m[i], v = ch.v[i];
+    adamw_elem(g, p, m, v, ch.wd, s);
+    uint32_t h;
+    if constexpr (kSR) {
+      const uint64_t gidx = ch.gidx + i;
+      const uint64_t blk = gidx >> 3;
+      const uint32_t ln = (uint32_t)(gidx & 7);
+      uint32_t w[4];
+      philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), step_lo, step_hi, seed_lo, seed_hi, w);
+      const uint32_t word = w[ln >> 1];
+      h = bf16_sr(p, (ln & 1) ? (word >> 16) : (word & 0xFFFFu));
+    } else {
+      h = bf16_rne(p);
+    }
+    ch.p[i] = p; ch.m[i] = m; ch.v[i] = v;
+    ch.p16[i] = (uint16_t)h;
+  }
+}
+
+// One CTA per SM.  Warp 8's first lane walks this CTA's chunks (blockIdx.x, + gridDim.x, ...),
+// copies each chunk's record into the stage's header and starts the four bulk copies (p, m, v,
+// g) that fill it; warps 0-7 wait for the stage, take their eight elements from shared memory,
+// hand the stage back and update + store from registers.
+template <bool kGradF32, bool kSR>
+__global__ void __launch_bounds__(kThreads + 32, 1)
+adamw_multi_kernel(const Chunk *__restrict__ chunks, uint32_t n_chunks, Scalars s, uint32_t seed_lo,
                    uint32_t seed_hi, uint32_t step_lo, uint32_t step_hi, uint32_t *status,
                    const Scalars *__restrict__ sched, const unsigned long long *__restrict__ counter,
                    unsigned long long sched_first, uint32_t sched_len) {
+  using R = Ring<kGradF32>;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t bars[2 * R::kStages];
   if (sched) {
     // device-resident schedule: the step number lives in device memory and selects this step's
     // scalars from a table the host filled in advance, so the launch can be replayed from a graph
@@ -94,78 +197,72 @@ adamw_multi_kernel(const TensorEntry *__restrict__ tensors, const Chunk *__restr
     step_lo = (uint32_t)t;
     step_hi = (uint32_t)(t >> 32);
   }
-  for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-    const Chunk ch = chunks[c];
-    if (ch.tensor >= n_tensors) {   // table corruption guard: record and skip
-      if (threadIdx.x == 0) atomicOr(status, ANC_DEV_BAD_INDEX);
-      continue;
+  const uint32_t full0 = anc_ring::smem_u32(&bars[0]), empty0 = anc_ring::smem_u32(&bars[R::kStages]);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R::kStages; ++i) {
+      anc_ring::mbar_init(full0 + 8 * i, 1);
+      anc_ring::mbar_init(empty0 + 8 * i, kThreads / 32);
     }
-    const TensorEntry t = tensors[ch.tensor];
-    const uint32_t groups = ch.count >> 3;           // full 8-element groups
-    if (t.vec_ok) {
-      for (uint32_t gi = threadIdx.x; gi < groups; gi += kThreads) {
-        const uint64_t i = ch.start + (uint64_t)gi * 8;
-        float g[8], p[8], m[8], v[8];
-        load_grad8<kGradF32>(t.g, i, g);
-        const float4 p0 = __ldcs(reinterpret_cast<const float4 *>(t.p + i));
-        const float4 p1 = __ldcs(reinterpret_cast<const float4 *>(t.p + i) + 1);
-        const float4 m0 = __ldcs(reinterpret_cast<const float4 *>(t.m + i));
-        const float4 m1 = __ldcs(reinterpret_cast<const float4 *>(t.m + i) + 1);
-        const float4 v0 = __ldcs(reinterpret_cast<const float4 *>(t.v + i));
-        const float4 v1 = __ldcs(reinterpret_cast<const float4 *>(t.v + i) + 1);
-        p[0] = p0.x; p[1] = p0.y; p[2] = p0.z; p[3] = p0.w; p[4] = p1.x; p[5] = p1.y; p[6] = p1.z; p[7] = p1.w;
-        m[0] = m0.x; m[1] = m0.y; m[2] = m0.z; m[3] = m0.w; m[4] = m1.x; m[5] = m1.y; m[6] = m1.z; m[7] = m1.w;
-        v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) adamw_elem(g[k], p[k], m[k], v[k], t.wd, s);
-        uint32_t h[8];
-        if constexpr (kSR) {
-          const uint64_t blk = (t.elem_offset + i) >> 3;
-          uint32_t w[4];
-          philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), step_lo, step_hi, seed_lo, seed_hi, w);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            h[2 * k] = bf16_sr(p[2 * k], w[k] & 0xFFFFu);
-            h[2 * k + 1] = bf16_sr(p[2 * k + 1], w[k] >> 16);
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) h[k] = bf16_rne(p[k]);
-        }
-        __stcs(reinterpret_cast<float4 *>(t.p + i), make_float4(p[0], p[1], p[2], p[3]));
-        __stcs(reinterpret_cast<float4 *>(t.p + i) + 1, make_float4(p[4], p[5], p[6], p[7]));
-        __stcs(reinterpret_cast<float4 *>(t.m + i), make_float4(m[0], m[1], m[2], m[3]));
-        __stcs(reinterpret_cast<float4 *>(t.m + i) + 1, make_float4(m[4], m[5], m[6], m[7]));
-        __stcs(reinterpret_cast<float4 *>(t.v + i), make_float4(v[0], v[1], v[2], v[3]));
-        __stcs(reinterpret_cast<float4 *>(t.v + i) + 1, make_float4(v[4], v[5], v[6], v[7]));
-        *reinterpret_cast<uint4 *>(t.p16 + i) =
-            make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+    anc_ring::mbar_init_fence();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kThreads / 32) {
+    if (lane != 0) return;
+    uint32_t it = 0;
+    uint32_t c = blockIdx.x;
+    Chunk nxt = chunks[c];                      // the grid never exceeds n_chunks
+    for (; c < n_chunks; c += gridDim.x, ++it) {
+      const Chunk ch = nxt;
+      if (c + gridDim.x < n_chunks) nxt = chunks[c + gridDim.x];
+      const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+      if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
+        atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        return;
       }
-    }
-    // scalar path: the ragged tail of a tensor, or a tensor whose pointers are not
-    // 16-byte aligned.  Same arithmetic, same Philox block per 8 elements.
-    const uint32_t first = t.vec_ok ? (groups << 3) : 0u;
-    for (uint32_t e = first + threadIdx.x; e < ch.count; e += kThreads) {
-      const uint64_t i = ch.start + e;
-      float g;
-      if constexpr (kGradF32) g = ((const float *)t.g)[i];
-      else g = __uint_as_float((uint32_t)((const uint16_t *)t.g)[i] << 16);
-      float p = t.p[i], m = t.m[i], v = t.v[i];
-      adamw_elem(g, p, m, v, t.wd, s);
-      uint32_t h;
-      if constexpr (kSR) {
-        const uint64_t gidx = t.elem_offset + i;
-        const uint64_t blk = gidx >> 3;
-        const uint32_t lane = (uint32_t)(gidx & 7);
-        uint32_t w[4];
-        philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), step_lo, step_hi, seed_lo, seed_hi, w);
-        const uint32_t word = w[lane >> 1];
-        h = bf16_sr(p, (lane & 1) ? (word >> 16) : (word & 0xFFFFu));
+      uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+      *reinterpret_cast<Chunk *>(st) = ch;
+      if (ch.bulk) {
+        const uint32_t dst = anc_ring::smem_u32(st + kHdrBytes);
+        anc_ring::mbar_expect_tx(full0 + 8 * slot, ch.count * (12u + R::kGradBytes));
+        anc_ring::bulk_load(dst, ch.p, ch.count * 4u, full0 + 8 * slot);
+        anc_ring::bulk_load(dst + kChunkElems * 4u, ch.m, ch.count * 4u, full0 + 8 * slot);
+        anc_ring::bulk_load(dst + kChunkElems * 8u, ch.v, ch.count * 4u, full0 + 8 * slot);
+        anc_ring::bulk_load(dst + kChunkElems * 12u, ch.g, ch.count * R::kGradBytes, full0 + 8 * slot);
       } else {
-        h = bf16_rne(p);
+        anc_ring::mbar_arrive(full0 + 8 * slot);
       }
-      t.p[i] = p; t.m[i] = m; t.v[i] = v;
-      t.p16[i] = (uint16_t)h;
+    }
+    return;
+  }
+  uint32_t it = 0;
+  for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x, ++it) {
+    const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+    if (!anc_ring::mbar_wait(full0 + 8 * slot, ph)) {
+      if (lane == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+      return;
+    }
+    const uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+    const Chunk ch = *reinterpret_cast<const Chunk *>(st);
+    if (ch.bulk) {
+      const int t = threadIdx.x;
+      const bool act = (uint32_t)t * 8u < ch.count;
+      float g[8], p[8], m[8], v[8];
+      if (act) {
+        const float *sp = reinterpret_cast<const float *>(st + kHdrBytes);
+        anc_ring::ld8(sp, t, lane, p);
+        anc_ring::ld8(sp + kChunkElems, t, lane, m);
+        anc_ring::ld8(sp + 2 * kChunkElems, t, lane, v);
+        if constexpr (kGradF32) anc_ring::ld8(sp + 3 * kChunkElems, t, lane, g);
+        else anc_ring::ld8_bf16(reinterpret_cast<const uint16_t *>(sp + 3 * kChunkElems), t, g);
+      }
+      __syncwarp();
+      if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
+      if (act) finish8<kSR>(ch, (uint32_t)t * 8u, g, p, m, v, s, seed_lo, seed_hi, step_lo, step_hi);
+    } else {
+      __syncwarp();
+      if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
+      direct_chunk<kGradF32, kSR>(ch, s, seed_lo, seed_hi, step_lo, step_hi);
     }
   }
 }
@@ -180,7 +277,6 @@ struct anc_adamw_plan {
   std::vector<TensorEntry> tensors;
   uint64_t arena_elems;     // max(elem_offset + numel)
   uint64_t owned_elems;
-  TensorEntry *d_tensors;
   Chunk *d_chunks;
   uint32_t n_chunks;
   uint32_t chunk_capacity;
@@ -199,11 +295,20 @@ static int adamw_build_chunks(anc_adamw_plan *pl, uint64_t begin, uint64_t end) 
     const uint64_t hi = (t.elem_offset + t.numel) < end ? (t.elem_offset + t.numel) : end;
     if (lo >= hi) continue;
     owned += hi - lo;
+    const uint32_t gb = pl->grad_dtype == ANC_GRAD_F32 ? 4u : 2u;
     for (uint64_t s = lo; s < hi; s += kChunkElems) {
+      const uint64_t first = s - t.elem_offset;       // inside the tensor, a multiple of 8
       Chunk c;
-      c.start = s - t.elem_offset;
-      c.tensor = ti;
+      c.g = (const uint8_t *)t.g + first * gb;
+      c.p = t.p + first;
+      c.m = t.m + first;
+      c.v = t.v + first;
+      c.p16 = t.p16 + first;
+      c.gidx = s;
       c.count = (uint32_t)((hi - s) < (uint64_t)kChunkElems ? (hi - s) : (uint64_t)kChunkElems);
+      c.wd = t.wd;
+      c.aligned = t.vec_ok;
+      c.bulk = (t.vec_ok && c.count % 8 == 0) ? 1u : 0u;
       chunks.push_back(c);
     }
   }
@@ -235,7 +340,6 @@ int anc_adamw_plan_create(anc_ctx *ctx, const anc_adamw_tensor *tensors, int n_t
   pl->ctx = ctx;
   pl->grad_dtype = grad_dtype;
   pl->arena_elems = 0;
-  pl->d_tensors = nullptr;
   pl->d_chunks = nullptr;
   pl->n_chunks = 0;
   pl->chunk_capacity = 0;
@@ -261,14 +365,21 @@ int anc_adamw_plan_create(anc_ctx *ctx, const anc_adamw_tensor *tensors, int n_t
     pl->tensors.push_back(t);
     if (a.elem_offset + a.numel > pl->arena_elems) pl->arena_elems = a.elem_offset + a.numel;
   }
-  if (n_tensors > 0) {
-    cudaError_t e = cudaMalloc((void **)&pl->d_tensors, sizeof(TensorEntry) * n_tensors);
-    if (e == cudaSuccess)
-      e = cudaMemcpy(pl->d_tensors, pl->tensors.data(), sizeof(TensorEntry) * n_tensors,
-                     cudaMemcpyHostToDevice);
+  {
+    // the ring's shared memory is above the default per-launch limit
+    cudaError_t e = cudaSuccess;
+#define ANC_ADAMW_SMEM(F32, SR)                                                                      \
+  if (e == cudaSuccess)                                                                              \
+    e = cudaFuncSetAttribute(adamw_multi_kernel<F32, SR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                             (int)Ring<F32>::kSmemBytes)
+    ANC_ADAMW_SMEM(true, true);
+    ANC_ADAMW_SMEM(true, false);
+    ANC_ADAMW_SMEM(false, true);
+    ANC_ADAMW_SMEM(false, false);
+#undef ANC_ADAMW_SMEM
     if (e != cudaSuccess) {
       delete pl;
-      return anc_cuda_fail(e, "adamw tensor table");
+      return anc_cuda_fail(e, "adamw kernel attributes");
     }
   }
   int rc = adamw_build_chunks(pl, 0, UINT64_MAX);
@@ -307,16 +418,13 @@ int anc_adamw_step(anc_adamw_plan *plan, const anc_adamw_scalars *sc, int roundi
   cudaStream_t st = anc_pick_stream(ctx, stream);
   Scalars s = {sc->beta1, sc->one_minus_beta1, sc->beta2, sc->one_minus_beta2,
                sc->eps,   sc->lr,              sc->ibc1,  sc->ibc2};
-  uint32_t grid = plan->n_chunks;
-  const uint32_t cap = (uint32_t)ctx->sm_count * 16u;
-  if (grid > cap) grid = cap;
-  const uint32_t nt = (uint32_t)plan->tensors.size();
+  uint32_t grid = plan->n_chunks;                   // one persistent CTA per SM
+  if (grid > (uint32_t)ctx->sm_count) grid = (uint32_t)ctx->sm_count;
   const uint32_t sl = (uint32_t)seed, sh = (uint32_t)(seed >> 32);
   const uint32_t tl = (uint32_t)step, th = (uint32_t)(step >> 32);
-#define ANC_ADAMW_LAUNCH(F32, SR)                                                              \
-  adamw_multi_kernel<F32, SR><<<grid, kThreads, 0, st>>>(plan->d_tensors, plan->d_chunks,      \
-                                                         plan->n_chunks, nt, s, sl, sh, tl, th, \
-                                                         ctx->d_status, nullptr, nullptr, 0ull, 0u)
+#define ANC_ADAMW_LAUNCH(F32, SR)                                                                  \
+  adamw_multi_kernel<F32, SR><<<grid, kThreads + 32, Ring<F32>::kSmemBytes, st>>>(                 \
+      plan->d_chunks, plan->n_chunks, s, sl, sh, tl, th, ctx->d_status, nullptr, nullptr, 0ull, 0u)
   const bool f32 = plan->grad_dtype == ANC_GRAD_F32;
   const bool sr = rounding == ANC_ROUND_SR;
   if (f32 && sr) ANC_ADAMW_LAUNCH(true, true);
@@ -371,14 +479,12 @@ int anc_adamw_step_scheduled(anc_adamw_plan *plan, int rounding, uint64_t seed, 
   if (plan->n_chunks) {
     Scalars s = {};
     uint32_t grid = plan->n_chunks;
-    const uint32_t cap = (uint32_t)ctx->sm_count * 16u;
-    if (grid > cap) grid = cap;
-    const uint32_t nt = (uint32_t)plan->tensors.size();
+    if (grid > (uint32_t)ctx->sm_count) grid = (uint32_t)ctx->sm_count;
     const uint32_t sl = (uint32_t)seed, sh = (uint32_t)(seed >> 32);
 #define ANC_ADAMW_LAUNCH_S(F32, SR)                                                                 \
-  adamw_multi_kernel<F32, SR><<<grid, kThreads, 0, st>>>(                                           \
-      plan->d_tensors, plan->d_chunks, plan->n_chunks, nt, s, sl, sh, 0u, 0u, ctx->d_status,        \
-      plan->d_sched, plan->d_counter, plan->sched_first, plan->sched_len)
+  adamw_multi_kernel<F32, SR><<<grid, kThreads + 32, Ring<F32>::kSmemBytes, st>>>(                  \
+      plan->d_chunks, plan->n_chunks, s, sl, sh, 0u, 0u, ctx->d_status, plan->d_sched,              \
+      plan->d_counter, plan->sched_first, plan->sched_len)
     const bool f32 = plan->grad_dtype == ANC_GRAD_F32;
     const bool sr = rounding == ANC_ROUND_SR;
     if (f32 && sr) ANC_ADAMW_LAUNCH_S(true, true);
@@ -401,7 +507,6 @@ int anc_adamw_plan_destroy(anc_adamw_plan *plan) {
   cudaStreamSynchronize(plan->ctx->stream);
   if (plan->d_sched) cudaFree(plan->d_sched);
   if (plan->d_counter) cudaFree(plan->d_counter);
-  if (plan->d_tensors) cudaFree(plan->d_tensors);
   if (plan->d_chunks) cudaFree(plan->d_chunks);
   delete plan;
   return ANC_OK;

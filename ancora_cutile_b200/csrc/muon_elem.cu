@@ -60,13 +60,20 @@ __device__ __forceinline__ float momentum_tile(const MomW &w, int slot, uint16_t
   // transposed store.
   const size_t flat0 = ((size_t)ti * (w.N / kTile) + tj) * (kTile * kTile) + (size_t)threadIdx.x * 8;
   float ss = 0.f;
+  // both rows' loads are issued before the first store: the stores could alias the second row's
+  // loads as far as the compiler knows, and a thread with 96 instead of 48 bytes in flight is
+  // what keeps HBM busy
+  size_t idxs[2];
+  float4 b0s[2], b1s[2];
+  float gs[2][8];
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
     const int rl = r0 + 32 * k;
     const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + col : flat0 + (size_t)k * (kThreads * 8);
-    const float4 b0 = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx));
-    const float4 b1 = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx) + 1);
-    float g[8];
+    idxs[k] = idx;
+    b0s[k] = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx));
+    b1s[k] = __ldcs(reinterpret_cast<const float4 *>(w.buf + idx) + 1);
+    float *g = gs[k];
     if constexpr (kGradF32) {
       const float4 g0 = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx));
       const float4 g1 = __ldcs(reinterpret_cast<const float4 *>((const float *)w.g + idx) + 1);
@@ -80,6 +87,13 @@ __device__ __forceinline__ float momentum_tile(const MomW &w, int slot, uint16_t
         g[2 * j + 1] = __uint_as_float(gw[j] & 0xFFFF0000u);
       }
     }
+  }
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int rl = r0 + 32 * k;
+    const size_t idx = idxs[k];
+    const float4 b0 = b0s[k], b1 = b1s[k];
+    const float *g = gs[k];
     const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
     float nb[8];
     uint32_t h[8];
@@ -125,6 +139,19 @@ __device__ __forceinline__ void update_tile(const UpdW &w, int slot, const uint1
   const int r0 = threadIdx.x >> 3;
   const int col = tj * kTile + c8;
   const size_t flat0 = ((size_t)ti * (w.N / kTile) + tj) * (kTile * kTile) + (size_t)threadIdx.x * 8;
+  // all global loads of both rows before the first store (see momentum_tile)
+  size_t idxs[2];
+  float4 p0s[2], p1s[2];
+  uint4 ovs[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int rl = r0 + 32 * k;
+    const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + col : flat0 + (size_t)k * (kThreads * 8);
+    idxs[k] = idx;
+    p0s[k] = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
+    p1s[k] = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx) + 1);
+    if (!w.tr) ovs[k] = *reinterpret_cast<const uint4 *>(wo + idx);
+  }
   if (w.tr) {
     // stage O^T tile: source rows = columns of the weight tile
     const int oc = threadIdx.x >> 2;
@@ -139,12 +166,11 @@ __device__ __forceinline__ void update_tile(const UpdW &w, int slot, const uint1
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
     const int rl = r0 + 32 * k;
-    const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + col : flat0 + (size_t)k * (kThreads * 8);
-    const float4 p0 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx));
-    const float4 p1 = __ldcs(reinterpret_cast<const float4 *>(w.p32 + idx) + 1);
+    const size_t idx = idxs[k];
+    const float4 p0 = p0s[k], p1 = p1s[k];
     float o[8];
     if (!w.tr) {
-      const uint4 ov = *reinterpret_cast<const uint4 *>(wo + idx);
+      const uint4 ov = ovs[k];
       const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {

@@ -1,0 +1,83 @@
+// Shared-memory staging ring of the HBM-bound sweeps (AdamW, Muon momentum / update): one
+// thread issues untiled bulk copies (cp.async.bulk, the 1-D form of TMA) several stages ahead,
+// their bytes complete an mbarrier per stage, the other warps wait on it, compute from shared
+// memory and store their results straight from registers.  The bytes in flight per SM are then
+// the ring's size (about 200 KB) instead of what the registers of the resident threads can hold,
+// and no load instruction of the computing warps ever waits for HBM.
+//
+// A bulk copy wants both addresses 16-byte aligned and a size that is a multiple of 16 bytes;
+// callers send anything else down a path with plain loads.  Every wait is bounded.
+#pragma once
+#include <stdint.h>
+
+namespace anc_ring {
+
+constexpr uint32_t kWaitTries = 1u << 19;   // each try may suspend ~2 us: about a second in all
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// the last operand is the time (ns) the hardware may keep the thread suspended in the instruction
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(2000u)
+      : "memory");
+  return ok != 0;
+}
+// false when the limit ran out
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kWaitTries; ++it)
+    if (mbar_try(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// barrier among the first `count` threads of the CTA (the computing warps), id 1
+__device__ __forceinline__ void bar_compute(int count) {
+  asm volatile("bar.sync 1, %0;" ::"r"(count) : "memory");
+}
+
+// Eight consecutive floats of a staged array, element index 8 * t, as two 16-byte reads.  A
+// quarter warp reading chunks 2t and 2t+1 in the same order would hit every bank group twice;
+// lanes 4-7 of each eight take the odd chunk first.
+__device__ __forceinline__ void ld8(const float *base, int t, int lane, float out[8]) {
+  const int sw = (lane >> 2) & 1;
+  const float4 *q = reinterpret_cast<const float4 *>(base) + 2 * t;
+  const float4 a = q[sw], b = q[sw ^ 1];
+  const float4 lo = sw ? b : a, hi = sw ? a : b;
+  out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+  out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+}
+// Eight consecutive bf16 values (one 16-byte read), widened.
+__device__ __forceinline__ void ld8_bf16(const uint16_t *base, int t, float out[8]) {
+  const uint4 r = reinterpret_cast<const uint4 *>(base)[t];
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    out[2 * k] = __uint_as_float(w[k] << 16);
+    out[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+  }
+}
+
+}  // namespace anc_ring
