@@ -73,17 +73,28 @@ int anc_launch_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O
                       float lr_scale, int transposed, cudaStream_t st);
 int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
                              cudaStream_t st);
-int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
-                              int elems_per_w, int grad_dtype, float momentum, int nesterov,
+// Storage of one CUtensorMap (kept opaque here so that this header needs no driver types).
+struct alignas(64) anc_tmap { unsigned char b[128]; };
+// Tiled map over a dense row-major array of `slices` matrices of (rows, inner) elements of 2 or 4
+// bytes (slices == 0: a single matrix, 2-D map), box (box_inner, box_rows[, 1]), no swizzle.
+int anc_encode_tile_map(anc_tmap *out, const void *ptr, int elem_bytes, uint64_t inner, uint64_t rows,
+                        uint64_t slices, uint32_t box_inner, uint32_t box_rows);
+// d_maps: three maps per table entry (momentum buffer, gradient, master weight; 64x64 boxes) for
+// the entries with tr != 0, unused storage for the others.
+int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, const anc_tmap *d_maps, uint16_t *xbase,
+                              int n_w, int elems_per_w, int grad_dtype, float momentum, int nesterov,
                               float *partial, cudaStream_t st);
+// partial: per matrix, per_matrix sums of squares (warp_sums == 0: fro_partial's blocks) or per_matrix
+// groups of eight warp sums (warp_sums != 0: the momentum kernel's 64x64 tiles).
 // sched (nullable): 2 + E scheduler words of the chain kernel, cleared here
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
-                            float eps, uint32_t *sched, cudaStream_t st);
+                            int warp_sums, float eps, uint32_t *sched, cudaStream_t st);
 int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int E, int M, int N,
                            cudaStream_t st);
-int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_extras, const uint16_t *obase,
-                            int n_w, int elems_per_w, float lr_scale_wide, float lr_scale_tall,
-                            cudaStream_t st);
+// omap: 3-D map over the packed operand at obase seen as slots of (N, K) bf16, 64x64 boxes (host copy).
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const anc_tmap *d_maps, const anc_tmap *omap,
+                            const void *d_extras, const uint16_t *obase, int n_w, int elems_per_w,
+                            float lr_scale_wide, float lr_scale_tall, cudaStream_t st);
 // mscale (nullable): per-matrix factor r[e] folded into the epilogue -- mode 0 stores
 // RNE(r^2 * acc), mode 2 stores RNE((alpha*r)*Q + (beta*r)*acc); mode 1 ignores it.
 // diag (mode 1): added to the diagonal of every matrix before the rounding (0 adds nothing).

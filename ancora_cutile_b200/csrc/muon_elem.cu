@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <mutex>
 #include "anc_internal.h"
+#include "stream_ring.cuh"
 
 namespace {
 
@@ -203,48 +204,12 @@ __device__ __forceinline__ float warp_tree_sum_f(float v) {
   return v;
 }
 
-// Sum of one tile over the CTA in a fixed order: thread -> warp shuffle tree -> the 8 warp
-// sums added in warp order by thread 0.
-__device__ __forceinline__ void tile_sumsq_store(float ss, float *dst, float *wsum) {
-  ss = warp_tree_sum_f(ss);
-  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = wsum[0];
-#pragma unroll
-    for (int k = 1; k < kThreads / 32; ++k) t = __fadd_rn(t, wsum[k]);
-    *dst = t;
-  }
-  __syncthreads();
-}
-
-// Table-driven launches: every weight in the table has the same K*N, hence the same
-// number of tiles (tiles_per_w); block b works on weight b / tiles_per_w.
-template <bool kGradF32>
-__global__ void __launch_bounds__(kThreads)
-momentum_kernel(const MomW *__restrict__ table, uint16_t *xbase, int n_w, int tiles_per_w, float mu,
-                int nesterov, float *__restrict__ partial) {
-  // partial[slot * tiles_per_w + tile] = sum of squares of that 64x64 tile of bf16 u
-  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
-  __shared__ float wsum[kThreads / 32];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // the packed operand may still be read by the previous launch
-  const int total = n_w * tiles_per_w;
-  for (int b = blockIdx.x; b < total; b += gridDim.x) {
-    const int wi = b / tiles_per_w;
-    const int t = b - wi * tiles_per_w;
-    const MomW w = table[wi];
-    const int tn = w.N / kTile;
-    const float ss = momentum_tile<kGradF32>(w, wi, xbase, t / tn, t % tn, mu, nesterov, sm);
-    if (partial) tile_sumsq_store(ss, partial + (size_t)wi * tiles_per_w + t, wsum);
-  }
-}
-
-// recip[e] = 1 / (sqrt(sum of the matrix's tile partials) + eps): one CTA per matrix,
-// thread-strided partial sums in index order, then the fixed tree.
+// recip[e] = 1 / (sqrt(sum of the matrix's tile sums) + eps): one CTA per matrix.  The momentum
+// kernel leaves eight warp sums per 64x64 tile; a tile's sum is those eight added in warp order,
+// the matrix's sum the tile sums added thread-strided in index order, then the fixed tree.
 __global__ void __launch_bounds__(kThreads)
 fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip, int per_matrix,
-                    float eps, uint32_t *sched) {
+                    int warp_sums, float eps, uint32_t *sched) {
   __shared__ float wsum[kThreads / 32];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -257,9 +222,23 @@ fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip
       sched[1] = 0u;
     }
   }
-  const float *pp = partial + (size_t)blockIdx.x * per_matrix;
   float acc = 0.f;
-  for (int k = threadIdx.x; k < per_matrix; k += kThreads) acc = __fadd_rn(acc, pp[k]);
+  if (!warp_sums) {   // one value per block of the matrix (fro_partial_kernel)
+    const float *p1 = partial + (size_t)blockIdx.x * per_matrix;
+    for (int k = threadIdx.x; k < per_matrix; k += kThreads) acc = __fadd_rn(acc, p1[k]);
+  }
+  const float4 *pp = reinterpret_cast<const float4 *>(partial) + (size_t)blockIdx.x * per_matrix * 2;
+  for (int k = threadIdx.x; warp_sums && k < per_matrix; k += kThreads) {
+    const float4 a = pp[2 * k], b = pp[2 * k + 1];
+    float t = __fadd_rn(a.x, a.y);
+    t = __fadd_rn(t, a.z);
+    t = __fadd_rn(t, a.w);
+    t = __fadd_rn(t, b.x);
+    t = __fadd_rn(t, b.y);
+    t = __fadd_rn(t, b.z);
+    t = __fadd_rn(t, b.w);
+    acc = __fadd_rn(acc, t);
+  }
   acc = warp_tree_sum_f(acc);
   if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
   __syncthreads();
@@ -271,21 +250,280 @@ fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip
   }
 }
 
-// lr_scale_wide applies to weights stored with K <= N, lr_scale_tall to K > N
-// (lr * sqrt(max(1, K/N)), ancora/optim/muon.py:101,176).
-__global__ void __launch_bounds__(kThreads)
-update_kernel(const UpdW *__restrict__ table, const uint16_t *obase, int n_w, int tiles_per_w,
-              float lr_scale_wide, float lr_scale_tall) {
+// ---- the two table-driven sweeps fed by a staging ring ------------------------------------
+// One CTA per SM: the first lane of warp 8 walks this CTA's tiles (blockIdx.x, + gridDim.x, ...) and
+// fills a ring of stages several tiles ahead: a flat tile is one untiled bulk copy per array, a tile
+// of a tall weight one 64x64 box per array through the weight's tensor maps (64 row-sized bulk
+// copies per array instead ran at a third of the speed: the copy engine takes about 60 cycles per
+// request whatever its size); warps 0-7 wait for a
+// stage, take their 16 elements from shared memory, hand the stage back, and compute and store
+// from registers with the arithmetic of momentum_tile / update_tile (the single-weight kernels).
+// Every weight in the table has the same K*N, hence the same number of tiles (tiles_per_w); tile b
+// belongs to weight b / tiles_per_w.  lr_scale_wide applies to weights stored with K <= N,
+// lr_scale_tall to K > N (lr * sqrt(max(1, K/N)), ancora/optim/muon.py:101,176).
+constexpr int kRingHdr = 128;                 // table entry + tile coordinates travel with the stage
+constexpr int kTileElems = kTile * kTile;
+template <int kBytesPerElem>
+struct TileRing {
+  static constexpr uint32_t kStageBytes = kRingHdr + kTileElems * kBytesPerElem;
+  static constexpr int kStages = (int)((200u * 1024u) / kStageBytes) > 7 ? 7 : (int)((200u * 1024u) / kStageBytes);
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 128;   // + room to align the base
+};
+__device__ __forceinline__ uint8_t *ring_base(uint8_t *raw) {
+  return raw + ((128u - (anc_ring::smem_u32(raw) & 127u)) & 127u);   // box loads want 128-byte aligned stages
+}
+
+template <bool kGradF32>
+__global__ void __launch_bounds__(kThreads + 32, 1)
+momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict__ maps, uint16_t *xbase, int n_w,
+                     int tiles_per_w, float mu, int nesterov, float *__restrict__ partial, uint32_t *status) {
+  using R = TileRing<kGradF32 ? 8 : 6>;
+  constexpr uint32_t kGB = kGradF32 ? 4u : 2u;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  uint8_t *ring = ring_base(ring_raw);
   __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ __align__(8) uint64_t bars[2 * R::kStages];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the packed operand may still be read by the previous launch
+  const uint32_t full0 = anc_ring::smem_u32(&bars[0]), empty0 = anc_ring::smem_u32(&bars[R::kStages]);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R::kStages; ++i) {
+      anc_ring::mbar_init(full0 + 8 * i, 1);
+      anc_ring::mbar_init(empty0 + 8 * i, kThreads / 32);
+    }
+    anc_ring::mbar_init_fence();
+  }
+  __syncthreads();
+  const int total = n_w * tiles_per_w;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kThreads / 32) {
+    if (lane != 0) return;
+    uint32_t it = 0;
+    int b = blockIdx.x;                                  // the grid never exceeds the tile count
+    MomW nxt = table[b / tiles_per_w];
+    for (; b < total; b += gridDim.x, ++it) {
+      const MomW w = nxt;
+      const int wi = b / tiles_per_w, t = b - wi * tiles_per_w;
+      if (b + (int)gridDim.x < total) nxt = table[(b + (int)gridDim.x) / tiles_per_w];
+      const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+      if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
+        atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        return;
+      }
+      const int tn = w.N / kTile, ti = t / tn, tj = t - ti * tn;
+      uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+      const uint32_t bar = full0 + 8 * slot;
+      *reinterpret_cast<MomW *>(st) = w;
+      *reinterpret_cast<int4 *>(st + 32) = make_int4(wi, t, ti, tj);
+      anc_ring::mbar_expect_tx(bar, kTileElems * (4u + kGB));
+      const uint32_t db = anc_ring::smem_u32(st + kRingHdr), dg = db + kTileElems * 4u;
+      if (!w.tr) {
+        const size_t flat = (size_t)t * kTileElems;
+        anc_ring::bulk_load(db, w.buf + flat, kTileElems * 4u, bar);
+        anc_ring::bulk_load(dg, (const uint8_t *)w.g + flat * kGB, kTileElems * kGB, bar);
+      } else {
+        const anc_tmap *m = maps + 3 * (size_t)wi;
+        anc_ring::box_load_2d(db, m, tj * kTile, ti * kTile, bar);
+        anc_ring::box_load_2d(dg, m + 1, tj * kTile, ti * kTile, bar);
+      }
+    }
+    return;
+  }
+  const int c8 = (threadIdx.x & 7) * 8;
+  const int r0 = threadIdx.x >> 3;
+  uint32_t it = 0;
+  for (int b = blockIdx.x; b < total; b += gridDim.x, ++it) {
+    const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+    const bool gave_up = !anc_ring::mbar_wait(full0 + 8 * slot, ph);
+    if (anc_ring::bar_compute_or(kThreads, gave_up)) {
+      if (gave_up && lane == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+      return;
+    }
+    const uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+    const MomW w = *reinterpret_cast<const MomW *>(st);
+    const int4 hv = *reinterpret_cast<const int4 *>(st + 32);
+    const int wi = hv.x, t = hv.y, ti = hv.z, tj = hv.w;
+    float bb[2][8], gg[2][8];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const float *sb = reinterpret_cast<const float *>(st + kRingHdr) + k * (kThreads * 8);
+      anc_ring::ld8(sb, threadIdx.x, lane, bb[k]);
+      if constexpr (kGradF32)
+        anc_ring::ld8(reinterpret_cast<const float *>(st + kRingHdr + kTileElems * 4) + k * (kThreads * 8),
+                      threadIdx.x, lane, gg[k]);
+      else
+        anc_ring::ld8_bf16(reinterpret_cast<const uint16_t *>(st + kRingHdr + kTileElems * 4) + k * (kThreads * 8),
+                           threadIdx.x, gg[k]);
+    }
+    __syncwarp();
+    if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
+    uint16_t *wx = xbase + (size_t)wi * w.K * w.N;
+    const size_t flat0 = (size_t)t * kTileElems + (size_t)threadIdx.x * 8;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int rl = r0 + 32 * k;
+      const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + (size_t)tj * kTile + c8
+                              : flat0 + (size_t)k * (kThreads * 8);
+      float nb[8];
+      uint32_t h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        nb[j] = __fadd_rn(__fmul_rn(mu, bb[k][j]), gg[k][j]);
+        const float u = nesterov ? __fadd_rn(gg[k][j], __fmul_rn(mu, nb[j])) : nb[j];
+        h[j] = rne16(u);
+        const float ur = bf16_f32(h[j]);
+        ss = __fadd_rn(ss, __fmul_rn(ur, ur));
+      }
+      __stcs(reinterpret_cast<float4 *>(w.buf + idx), make_float4(nb[0], nb[1], nb[2], nb[3]));
+      __stcs(reinterpret_cast<float4 *>(w.buf + idx) + 1, make_float4(nb[4], nb[5], nb[6], nb[7]));
+      const uint4 pk = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16),
+                                  h[6] | (h[7] << 16));
+      if (!w.tr) *reinterpret_cast<uint4 *>(wx + idx) = pk;
+      else *reinterpret_cast<uint4 *>(&sm[rl][swz_col(rl, c8)]) = pk;
+    }
+    if (w.tr) {
+      anc_ring::bar_compute(kThreads);
+      const int oc = threadIdx.x >> 2;
+      const int rr = (threadIdx.x & 3) * 16;
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int ra = rr + 2 * j;
+        const int sc = swz_col(ra, oc);
+        pk[j] = (uint32_t)sm[ra][sc] | ((uint32_t)sm[ra + 1][sc] << 16);
+      }
+      uint16_t *dst = wx + (size_t)(tj * kTile + oc) * w.K + (size_t)ti * kTile + rr;
+      reinterpret_cast<uint4 *>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      reinterpret_cast<uint4 *>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      // the next tile's vote barrier keeps its writes to the transposition tile behind these reads
+    }
+    if (partial) {
+      // partial[(slot * tiles_per_w + tile) * 8 + warp]: the warp's sum of squares of its bf16 u values
+      // (thread sums in element order, then the shuffle tree); the finalize kernel adds the eight
+      ss = warp_tree_sum_f(ss);
+      if (lane == 0) partial[((size_t)wi * tiles_per_w + t) * 8 + warp] = ss;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads + 32, 1)
+update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ maps,
+                   const __grid_constant__ anc_tmap omap, const uint16_t *obase, int n_w, int tiles_per_w,
+                   float lr_scale_wide, float lr_scale_tall, uint32_t *status) {
+  using R = TileRing<6>;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  uint8_t *ring = ring_base(ring_raw);
+  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ __align__(8) uint64_t bars[2 * R::kStages];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t full0 = anc_ring::smem_u32(&bars[0]), empty0 = anc_ring::smem_u32(&bars[R::kStages]);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R::kStages; ++i) {
+      anc_ring::mbar_init(full0 + 8 * i, 1);
+      anc_ring::mbar_init(empty0 + 8 * i, kThreads / 32);
+    }
+    anc_ring::mbar_init_fence();
+  }
+  __syncthreads();
   const int total = n_w * tiles_per_w;
-  for (int b = blockIdx.x; b < total; b += gridDim.x) {
-    const int wi = b / tiles_per_w;
-    const int t = b - wi * tiles_per_w;
-    const UpdW w = table[wi];
-    const int tn = w.N / kTile;
-    update_tile(w, wi, obase, w.tr ? lr_scale_tall : lr_scale_wide, t / tn, t % tn, sm);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kThreads / 32) {
+    if (lane != 0) return;
+    uint32_t it = 0;
+    int b = blockIdx.x;
+    UpdW nxt = table[b / tiles_per_w];
+    for (; b < total; b += gridDim.x, ++it) {
+      const UpdW w = nxt;
+      const int wi = b / tiles_per_w, t = b - wi * tiles_per_w;
+      if (b + (int)gridDim.x < total) nxt = table[(b + (int)gridDim.x) / tiles_per_w];
+      const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+      if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
+        atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        return;
+      }
+      const int tn = w.N / kTile, ti = t / tn, tj = t - ti * tn;
+      uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+      const uint32_t bar = full0 + 8 * slot;
+      *reinterpret_cast<UpdW *>(st) = w;
+      *reinterpret_cast<int4 *>(st + 32) = make_int4(wi, t, ti, tj);
+      anc_ring::mbar_expect_tx(bar, kTileElems * 6u);
+      const uint32_t dp = anc_ring::smem_u32(st + kRingHdr), dO = dp + kTileElems * 4u;
+      if (!w.tr) {
+        const size_t flat = (size_t)t * kTileElems;
+        anc_ring::bulk_load(dp, w.p32 + flat, kTileElems * 4u, bar);
+        anc_ring::bulk_load(dO, obase + (size_t)wi * w.K * w.N + flat, kTileElems * 2u, bar);
+      } else {
+        // the weight's tile, and the same tile of O^T: its rows are the tile's columns
+        anc_ring::box_load_2d(dp, maps + 3 * (size_t)wi + 2, tj * kTile, ti * kTile, bar);
+        anc_ring::box_load_3d(dO, &omap, ti * kTile, tj * kTile, wi, bar);
+      }
+    }
+    return;
+  }
+  const int c8 = (threadIdx.x & 7) * 8;
+  const int r0 = threadIdx.x >> 3;
+  uint32_t it = 0;
+  for (int b = blockIdx.x; b < total; b += gridDim.x, ++it) {
+    const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
+    const bool gave_up = !anc_ring::mbar_wait(full0 + 8 * slot, ph);
+    if (anc_ring::bar_compute_or(kThreads, gave_up)) {
+      if (gave_up && lane == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+      return;
+    }
+    const uint8_t *st = ring + (size_t)slot * R::kStageBytes;
+    const UpdW w = *reinterpret_cast<const UpdW *>(st);
+    const int4 hv = *reinterpret_cast<const int4 *>(st + 32);
+    const int t = hv.y, ti = hv.z, tj = hv.w;
+    const float lr_scale = w.tr ? lr_scale_tall : lr_scale_wide;
+    float pp[2][8], oo[2][8];
+    const uint16_t *sO = reinterpret_cast<const uint16_t *>(st + kRingHdr + kTileElems * 4);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      anc_ring::ld8(reinterpret_cast<const float *>(st + kRingHdr) + k * (kThreads * 8), threadIdx.x, lane, pp[k]);
+      if (!w.tr) anc_ring::ld8_bf16(sO + k * (kThreads * 8), threadIdx.x, oo[k]);
+    }
+    if (w.tr) {
+      // staged O^T tile (row oc = the weight tile's column oc) into the swizzled transposition tile
+      const int oc = threadIdx.x >> 2;
+      const int rr = (threadIdx.x & 3) * 16;
+      const int sw = (lane >> 2) & 1;
+      const uint4 *q = reinterpret_cast<const uint4 *>(sO + oc * kTile + rr);
+      const uint4 a = q[sw], c = q[sw ^ 1];
+      *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr + 8 * sw)]) = a;
+      *reinterpret_cast<uint4 *>(&sm[oc][swz_col(oc, rr + 8 * (sw ^ 1))]) = c;
+    }
+    __syncwarp();
+    if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
+    if (w.tr) {
+      anc_ring::bar_compute(kThreads);
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int rl = r0 + 32 * k;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oo[k][j] = bf16_f32(sm[c8 + j][swz_col(c8 + j, rl)]);
+      }
+    }
+    const size_t flat0 = (size_t)t * kTileElems + (size_t)threadIdx.x * 8;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int rl = r0 + 32 * k;
+      const size_t idx = w.tr ? (size_t)(ti * kTile + rl) * w.N + (size_t)tj * kTile + c8
+                              : flat0 + (size_t)k * (kThreads * 8);
+      float pn[8];
+      uint32_t h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        pn[j] = __fsub_rn(pp[k][j], __fmul_rn(lr_scale, oo[k][j]));
+        h[j] = rne16(pn[j]);
+      }
+      __stcs(reinterpret_cast<float4 *>(w.p32 + idx), make_float4(pn[0], pn[1], pn[2], pn[3]));
+      __stcs(reinterpret_cast<float4 *>(w.p32 + idx) + 1, make_float4(pn[4], pn[5], pn[6], pn[7]));
+      *reinterpret_cast<uint4 *>(w.p16 + idx) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16),
+                                                           h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+    }
+    // the next tile's vote barrier keeps its writes to the transposition tile behind these reads
   }
 }
 
@@ -642,11 +880,12 @@ static_assert(sizeof(anc_upd_entry) == sizeof(UpdW), "table layout");
 
 // Launch with programmatic stream serialization (the kernels above wait with griddepcontrol).
 template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t st, Args... args) {
+static cudaError_t launch_pdl_ex(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
+                                 Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -655,12 +894,34 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t s
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t st, Args... args) {
+  return launch_pdl_ex(kernel, grid, kThreads, 0, st, args...);
+}
+
+// The ring kernels' shared memory is above the default per-launch limit: raised once per device.
+static cudaError_t ring_kernels_ready(int device) {
+  static std::mutex mu;
+  static bool done[64] = {};
+  std::lock_guard<std::mutex> lock(mu);
+  if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(momentum_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)TileRing<8>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(momentum_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)TileRing<6>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(update_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)TileRing<6>::kSmemBytes);
+  if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
+  return e;
+}
 
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
-                            float eps, uint32_t *sched, cudaStream_t st) {
+                            int warp_sums, float eps, uint32_t *sched, cudaStream_t st) {
   (void)ctx;
   if (E <= 0) return ANC_OK;
-  ANC_CUDA(launch_pdl(fro_finalize_kernel, E, st, partial, recip, per_matrix, eps, sched));
+  ANC_CUDA(launch_pdl(fro_finalize_kernel, E, st, partial, recip, per_matrix, warp_sums, eps, sched));
   return ANC_OK;
 }
 
@@ -675,27 +936,30 @@ int anc_launch_fro_partial(anc_ctx *ctx, const uint16_t *X, float *partial, int 
   return ANC_OK;
 }
 
-int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, uint16_t *xbase, int n_w,
-                              int elems_per_w, int grad_dtype, float momentum, int nesterov,
+int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, const anc_tmap *d_maps, uint16_t *xbase,
+                              int n_w, int elems_per_w, int grad_dtype, float momentum, int nesterov,
                               float *partial, cudaStream_t st) {
   const int tpw = elems_per_w / (kTile * kTile);
   const long long total = (long long)n_w * tpw;
-  int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
+  int grid = (int)(total < (long long)ctx->sm_count ? total : (long long)ctx->sm_count);   // one CTA per SM
   if (grid == 0) return ANC_OK;
+  ANC_CUDA(ring_kernels_ready(ctx->device));
   if (grad_dtype == ANC_GRAD_F32)
-    ANC_CUDA(launch_pdl(momentum_kernel<true>, grid, st, (const MomW *)d_table, xbase, n_w, tpw, momentum,
-                        nesterov, partial));
+    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<true>, grid, kThreads + 32, TileRing<8>::kSmemBytes, st,
+                           (const MomW *)d_table, d_maps, xbase, n_w, tpw, momentum, nesterov, partial,
+                           ctx->d_status));
   else
-    ANC_CUDA(launch_pdl(momentum_kernel<false>, grid, st, (const MomW *)d_table, xbase, n_w, tpw, momentum,
-                        nesterov, partial));
+    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<false>, grid, kThreads + 32, TileRing<6>::kSmemBytes, st,
+                           (const MomW *)d_table, d_maps, xbase, n_w, tpw, momentum, nesterov, partial,
+                           ctx->d_status));
   return ANC_OK;
 }
 
 static_assert(sizeof(anc_upd_extra) == sizeof(UpdX), "table layout");
 
-int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_extras, const uint16_t *obase,
-                            int n_w, int elems_per_w, float lr_scale_wide, float lr_scale_tall,
-                            cudaStream_t st) {
+int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const anc_tmap *d_maps, const anc_tmap *omap,
+                            const void *d_extras, const uint16_t *obase, int n_w, int elems_per_w,
+                            float lr_scale_wide, float lr_scale_tall, cudaStream_t st) {
   if (d_extras) {
     const int tpw = elems_per_w / (kTile * kTile);
     const long long total = (long long)n_w * tpw;
@@ -707,10 +971,12 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const void *d_ext
   }
   const int tpw = elems_per_w / (kTile * kTile);
   const long long total = (long long)n_w * tpw;
-  int grid = (int)(total < (long long)ctx->sm_count * 8 ? total : (long long)ctx->sm_count * 8);
+  int grid = (int)(total < (long long)ctx->sm_count ? total : (long long)ctx->sm_count);   // one CTA per SM
   if (grid == 0) return ANC_OK;
-  ANC_CUDA(launch_pdl(update_kernel, grid, st, (const UpdW *)d_table, obase, n_w, tpw, lr_scale_wide,
-                      lr_scale_tall));
+  ANC_CUDA(ring_kernels_ready(ctx->device));
+  ANC_CUDA(launch_pdl_ex(update_ring_kernel, grid, kThreads + 32, TileRing<6>::kSmemBytes, st,
+                         (const UpdW *)d_table, d_maps, *omap, obase, n_w, tpw, lr_scale_wide, lr_scale_tall,
+                         ctx->d_status));
   return ANC_OK;
 }
 

@@ -20,6 +20,9 @@ struct Group {
   anc_mom_entry *d_mom = nullptr;  // device tables, one entry per weight
   anc_upd_entry *d_upd = nullptr;
   anc_upd_extra *d_ext = nullptr;  // optional extra outputs of the update (nullptr: none in this group)
+  anc_tmap *d_maps = nullptr;      // three 64x64-box tensor maps per weight (momentum buffer, gradient, master
+                                   // weight): how the sweeps fetch the tiles of tall (K > N) weights
+  anc_tmap omap[2];                // the packed operands X and Y seen as slots of (M, Nn) bf16, for the same sweeps
   double scale_tall = 1.0;         // sqrt(max(1, K/N)) for the K > N members
 };
 
@@ -81,6 +84,7 @@ static int ns_chain(anc_ctx *ctx, uint16_t *&X, uint16_t *A, uint16_t *B, uint16
 
 static void plan_free(anc_muon_plan *pl) {
   for (auto &g : pl->groups) {
+    if (g.d_maps) cudaFree(g.d_maps);
     if (g.d_mom) cudaFree(g.d_mom);
     if (g.d_upd) cudaFree(g.d_upd);
     if (g.d_ext) cudaFree(g.d_ext);
@@ -165,9 +169,20 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     std::vector<anc_mom_entry> mom;
     std::vector<anc_upd_entry> upd;
     std::vector<anc_upd_extra> ext;
+    std::vector<anc_tmap> maps(3 * g.widx.size());
     bool any_ext = false;
     for (size_t s = 0; s < g.widx.size(); ++s) {
       const anc_muon_weight &w = pl->weights[g.widx[s]];
+      if (w.K > w.N) {
+        const int gb = grad_dtype == ANC_GRAD_F32 ? 4 : 2;
+        int rc = anc_encode_tile_map(&maps[3 * s], w.buf, 4, (uint64_t)w.N, (uint64_t)w.K, 0, 64, 64);
+        if (!rc) rc = anc_encode_tile_map(&maps[3 * s + 1], w.g, gb, (uint64_t)w.N, (uint64_t)w.K, 0, 64, 64);
+        if (!rc) rc = anc_encode_tile_map(&maps[3 * s + 2], w.p32, 4, (uint64_t)w.N, (uint64_t)w.K, 0, 64, 64);
+        if (rc) {
+          plan_free(pl);
+          return rc;
+        }
+      }
       mom.push_back({w.buf, w.g, w.K, w.N, w.K > w.N ? 1 : 0, 0});
       upd.push_back({w.p32, w.p16, w.K, w.N, w.K > w.N ? 1 : 0, 0});
       const anc_muon_outputs &o = pl->outputs[g.widx[s]];
@@ -185,6 +200,9 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     }
     cudaError_t e = cudaMalloc((void **)&g.d_mom, mom.size() * sizeof(anc_mom_entry));
     if (e == cudaSuccess) e = cudaMalloc((void **)&g.d_upd, upd.size() * sizeof(anc_upd_entry));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&g.d_maps, maps.size() * sizeof(anc_tmap));
+    if (e == cudaSuccess)
+      e = cudaMemcpy(g.d_maps, maps.data(), maps.size() * sizeof(anc_tmap), cudaMemcpyHostToDevice);
     if (e == cudaSuccess)
       e = cudaMemcpy(g.d_mom, mom.data(), mom.size() * sizeof(anc_mom_entry), cudaMemcpyHostToDevice);
     if (e == cudaSuccess)
@@ -200,13 +218,22 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->A, ae * 2);
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->B, ae * 2);
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->recip, emax * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial, (xe / 4096) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&pl->partial, (xe / 4096) * 8 * sizeof(float));   // 8 warp sums per 64x64 tile
     if (e == cudaSuccess) e = cudaMalloc((void **)&pl->sched, (emax + 2) * sizeof(uint32_t));
     if (e != cudaSuccess) {
       plan_free(pl);
       return anc_cuda_fail(e, "muon scratch");
     }
-    pl->scratch_bytes = 4 * xe + 4 * ae + emax * sizeof(float) + (xe / 4096) * sizeof(float);
+    pl->scratch_bytes = 4 * xe + 4 * ae + emax * sizeof(float) + (xe / 4096) * 8 * sizeof(float);
+    for (auto &g : pl->groups) {
+      const size_t E = pl->max_batch > 0 ? std::min<size_t>(pl->max_batch, g.widx.size()) : g.widx.size();
+      int rc = anc_encode_tile_map(&g.omap[0], pl->X, 2, (uint64_t)g.Nn, (uint64_t)g.M, E, 64, 64);
+      if (!rc) rc = anc_encode_tile_map(&g.omap[1], pl->Y, 2, (uint64_t)g.Nn, (uint64_t)g.M, E, 64, 64);
+      if (rc) {
+        plan_free(pl);
+        return rc;
+      }
+    }
   }
   *out = pl;
   return ANC_OK;
@@ -256,13 +283,13 @@ int step_chunk(anc_muon_plan *pl, const ChunkRef &c, double lr, float momentum, 
   const int E = c.count;
   uint16_t *X = pl->X, *Y = pl->Y;
   begin_span(0);
-  int rc = anc_launch_momentum_group(ctx, g.d_mom + c.w0, X, E, epw, pl->grad_dtype, momentum, nesterov,
-                                     pl->partial, st);
+  int rc = anc_launch_momentum_group(ctx, g.d_mom + c.w0, g.d_maps + 3 * (size_t)c.w0, X, E, epw, pl->grad_dtype,
+                                     momentum, nesterov, pl->partial, st);
   end_span();
   if (rc) return rc;
   begin_span(1);
   if (ns_steps > 0)   // 1/(||u||_F + eps) per matrix from the momentum kernel's tile sums
-    rc = anc_launch_fro_finalize(ctx, pl->partial, pl->recip, E, epw / 4096, eps, pl->sched, st);
+    rc = anc_launch_fro_finalize(ctx, pl->partial, pl->recip, E, epw / 4096, 1, eps, pl->sched, st);
   else                // no iteration to fold the factor into: normalise in place
     rc = anc_launch_fro_normalize(ctx, X, pl->recip, E, g.M, g.Nn, eps, st);
   end_span();
@@ -284,8 +311,9 @@ int step_chunk(anc_muon_plan *pl, const ChunkRef &c, double lr, float momentum, 
   }
   pl->last_launches += (ns_steps > 0 && anc_ns_chain_supported(ctx, g.M, g.Nn, ns_steps)) ? 1 : 3 * ns_steps;
   begin_span(3);
-  rc = anc_launch_update_group(ctx, g.d_upd + c.w0, g.d_ext ? (const void *)(g.d_ext + c.w0) : nullptr, X, E,
-                               epw, scale_wide, scale_tall, st);
+  rc = anc_launch_update_group(ctx, g.d_upd + c.w0, g.d_maps + 3 * (size_t)c.w0, &g.omap[X == pl->X ? 0 : 1],
+                               g.d_ext ? (const void *)(g.d_ext + c.w0) : nullptr, X, E, epw, scale_wide,
+                               scale_tall, st);
   end_span();
   return rc;
 }
@@ -417,7 +445,7 @@ int anc_ns_batched_ex(anc_ctx *ctx, uint16_t *X, uint16_t *A, uint16_t *B, uint1
   int rc = anc_launch_fro_partial(ctx, X, (float *)ctx->d_work, E, M, N, st);
   if (rc) return rc;
   uint32_t *sched = (uint32_t *)((char *)ctx->d_work + sched_off);
-  rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, eps, sched, st);
+  rc = anc_launch_fro_finalize(ctx, (const float *)ctx->d_work, recip, E, (int)bpm, 0, eps, sched, st);
   if (rc) return rc;
   uint16_t *x = X, *y = Y;
   rc = ns_chain(ctx, x, A, B, y, E, M, N, steps, coeffs, recip, single_launch ? sched : nullptr, st);

@@ -1409,6 +1409,40 @@ int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, ui
   return ANC_OK;
 }
 
+}  // namespace
+
+int anc_encode_tile_map(anc_tmap *out, const void *ptr, int elem_bytes, uint64_t inner, uint64_t rows,
+                        uint64_t slices, uint32_t box_inner, uint32_t box_rows) {
+  static_assert(sizeof(anc_tmap) == sizeof(CUtensorMap), "tensor map storage");
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    anc_set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return ANC_E_CUDA;
+  }
+  const uint64_t eb = (uint64_t)elem_bytes;
+  if ((elem_bytes != 2 && elem_bytes != 4) || ((uintptr_t)ptr & 15) != 0 || (inner * eb) % 16 != 0 ||
+      (box_inner * eb) % 16 != 0 || box_inner > 256 || box_rows > 256) {
+    anc_set_error("tile map: operand must be 16-byte aligned with 16-byte multiple rows and boxes");
+    return ANC_E_INVALID;
+  }
+  cuuint64_t dims[3] = {inner, rows, slices ? slices : 1};
+  cuuint64_t strides[2] = {inner * eb, inner * rows * eb};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(reinterpret_cast<CUtensorMap *>(out),
+                   elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                   slices ? 3 : 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    anc_set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return ANC_E_CUDA;
+  }
+  return ANC_OK;
+}
+
+namespace {
+
 struct TileTab {
   uint32_t *d_tab;
   int count;

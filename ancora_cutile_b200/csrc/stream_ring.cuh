@@ -53,9 +53,39 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+// One 2-D / 3-D box of a tiled tensor map that lives in global memory (written by the host before
+// the launch).  The innermost coordinate times the element size must be a multiple of 16 bytes
+// and the destination 128-byte aligned.
+__device__ __forceinline__ void box_load_2d(uint32_t dst, const void *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void box_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
 // barrier among the first `count` threads of the CTA (the computing warps), id 1
 __device__ __forceinline__ void bar_compute(int count) {
   asm volatile("bar.sync 1, %0;" ::"r"(count) : "memory");
+}
+
+// The same barrier with an OR over a predicate: every computing warp learns whether any of them
+// gave up its wait, so that they leave together and nobody is left standing at a later barrier.
+__device__ __forceinline__ bool bar_compute_or(int count, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %2, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, %1, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
 }
 
 // Eight consecutive floats of a staged array, element index 8 * t, as two 16-byte reads.  A
