@@ -251,16 +251,19 @@ fro_finalize_kernel(const float *__restrict__ partial, float *__restrict__ recip
 }
 
 // ---- the two table-driven sweeps fed by a staging ring ------------------------------------
-// One CTA per SM: the first lane of warp 8 walks this CTA's tiles (blockIdx.x, + gridDim.x, ...) and
+// One CTA per SM: the first lane of the last warp walks this CTA's tiles (blockIdx.x, + gridDim.x, ...) and
 // fills a ring of stages several tiles ahead: a flat tile is one untiled bulk copy per array, a tile
 // of a tall weight one 64x64 box per array through the weight's tensor maps (64 row-sized bulk
 // copies per array instead ran at a third of the speed: the copy engine takes about 60 cycles per
-// request whatever its size); warps 0-7 wait for a
+// request whatever its size); one or two groups of eight computing warps take the stages in turn: wait for a
 // stage, take their 16 elements from shared memory, hand the stage back, and compute and store
 // from registers with the arithmetic of momentum_tile / update_tile (the single-weight kernels).
 // Every weight in the table has the same K*N, hence the same number of tiles (tiles_per_w); tile b
 // belongs to weight b / tiles_per_w.  lr_scale_wide applies to weights stored with K <= N,
 // lr_scale_tall to K > N (lr * sqrt(max(1, K/N)), ancora/optim/muon.py:101,176).
+// groups of 256 computing threads taking the stages in turn
+constexpr int kMomGroups = 2;                 // measured: momentum 0.97 against 1.02 ms per step with two groups,
+constexpr int kUpdGroups = 1;                 //           update 0.90 against 0.93 ms with one
 constexpr int kRingHdr = 128;                 // table entry + tile coordinates travel with the stage
 constexpr int kTileElems = kTile * kTile;
 template <int kBytesPerElem>
@@ -273,15 +276,15 @@ __device__ __forceinline__ uint8_t *ring_base(uint8_t *raw) {
   return raw + ((128u - (anc_ring::smem_u32(raw) & 127u)) & 127u);   // box loads want 128-byte aligned stages
 }
 
-template <bool kGradF32>
-__global__ void __launch_bounds__(kThreads + 32, 1)
+template <bool kGradF32, int kGroups>
+__global__ void __launch_bounds__(kGroups * kThreads + 32, 1)
 momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict__ maps, uint16_t *xbase, int n_w,
                      int tiles_per_w, float mu, int nesterov, float *__restrict__ partial, uint32_t *status) {
   using R = TileRing<kGradF32 ? 8 : 6>;
   constexpr uint32_t kGB = kGradF32 ? 4u : 2u;
   extern __shared__ __align__(128) uint8_t ring_raw[];
   uint8_t *ring = ring_base(ring_raw);
-  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ __align__(16) uint16_t sm2[kGroups][kTile][kTile + kPad];
   __shared__ __align__(8) uint64_t bars[2 * R::kStages];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // the packed operand may still be read by the previous launch
@@ -296,7 +299,7 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
   __syncthreads();
   const int total = n_w * tiles_per_w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == kThreads / 32) {
+  if (warp == kGroups * kThreads / 32) {
     if (lane != 0) return;
     uint32_t it = 0;
     int b = blockIdx.x;                                  // the grid never exceeds the tile count
@@ -329,13 +332,17 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
     }
     return;
   }
-  const int c8 = (threadIdx.x & 7) * 8;
-  const int r0 = threadIdx.x >> 3;
-  uint32_t it = 0;
-  for (int b = blockIdx.x; b < total; b += gridDim.x, ++it) {
+  const int grp = warp / (kThreads / 32);                 // this warp's group of 256 threads
+  const int tid = threadIdx.x & (kThreads - 1);           // thread within the group
+  const int wig = warp & (kThreads / 32 - 1);             // warp within the group
+  uint16_t (*sm)[kTile + kPad] = sm2[grp];
+  const int c8 = (tid & 7) * 8;
+  const int r0 = tid >> 3;
+  uint32_t it = grp;
+  for (int b = blockIdx.x + grp * (int)gridDim.x; b < total; b += kGroups * (int)gridDim.x, it += kGroups) {
     const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
     const bool gave_up = !anc_ring::mbar_wait(full0 + 8 * slot, ph);
-    if (anc_ring::bar_compute_or(kThreads, gave_up)) {
+    if (anc_ring::bar_compute_or(1 + grp, kThreads, gave_up)) {
       if (gave_up && lane == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
       return;
     }
@@ -347,18 +354,18 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const float *sb = reinterpret_cast<const float *>(st + kRingHdr) + k * (kThreads * 8);
-      anc_ring::ld8(sb, threadIdx.x, lane, bb[k]);
+      anc_ring::ld8(sb, tid, lane, bb[k]);
       if constexpr (kGradF32)
         anc_ring::ld8(reinterpret_cast<const float *>(st + kRingHdr + kTileElems * 4) + k * (kThreads * 8),
-                      threadIdx.x, lane, gg[k]);
+                      tid, lane, gg[k]);
       else
         anc_ring::ld8_bf16(reinterpret_cast<const uint16_t *>(st + kRingHdr + kTileElems * 4) + k * (kThreads * 8),
-                           threadIdx.x, gg[k]);
+                           tid, gg[k]);
     }
     __syncwarp();
     if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
     uint16_t *wx = xbase + (size_t)wi * w.K * w.N;
-    const size_t flat0 = (size_t)t * kTileElems + (size_t)threadIdx.x * 8;
+    const size_t flat0 = (size_t)t * kTileElems + (size_t)tid * 8;
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
@@ -383,9 +390,9 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
       else *reinterpret_cast<uint4 *>(&sm[rl][swz_col(rl, c8)]) = pk;
     }
     if (w.tr) {
-      anc_ring::bar_compute(kThreads);
-      const int oc = threadIdx.x >> 2;
-      const int rr = (threadIdx.x & 3) * 16;
+      anc_ring::bar_compute(1 + grp, kThreads);
+      const int oc = tid >> 2;
+      const int rr = (tid & 3) * 16;
       uint32_t pk[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -402,19 +409,20 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
       // partial[(slot * tiles_per_w + tile) * 8 + warp]: the warp's sum of squares of its bf16 u values
       // (thread sums in element order, then the shuffle tree); the finalize kernel adds the eight
       ss = warp_tree_sum_f(ss);
-      if (lane == 0) partial[((size_t)wi * tiles_per_w + t) * 8 + warp] = ss;
+      if (lane == 0) partial[((size_t)wi * tiles_per_w + t) * 8 + wig] = ss;
     }
   }
 }
 
-__global__ void __launch_bounds__(kThreads + 32, 1)
+template <int kGroups>
+__global__ void __launch_bounds__(kGroups * kThreads + 32, 1)
 update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ maps,
                    const __grid_constant__ anc_tmap omap, const uint16_t *obase, int n_w, int tiles_per_w,
                    float lr_scale_wide, float lr_scale_tall, uint32_t *status) {
   using R = TileRing<6>;
   extern __shared__ __align__(128) uint8_t ring_raw[];
   uint8_t *ring = ring_base(ring_raw);
-  __shared__ __align__(16) uint16_t sm[kTile][kTile + kPad];
+  __shared__ __align__(16) uint16_t sm2[kGroups][kTile][kTile + kPad];
   __shared__ __align__(8) uint64_t bars[2 * R::kStages];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -429,7 +437,7 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
   __syncthreads();
   const int total = n_w * tiles_per_w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == kThreads / 32) {
+  if (warp == kGroups * kThreads / 32) {
     if (lane != 0) return;
     uint32_t it = 0;
     int b = blockIdx.x;
@@ -462,13 +470,16 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
     }
     return;
   }
-  const int c8 = (threadIdx.x & 7) * 8;
-  const int r0 = threadIdx.x >> 3;
-  uint32_t it = 0;
-  for (int b = blockIdx.x; b < total; b += gridDim.x, ++it) {
+  const int grp = warp / (kThreads / 32);                 // this warp's group of 256 threads
+  const int tid = threadIdx.x & (kThreads - 1);           // thread within the group
+  uint16_t (*sm)[kTile + kPad] = sm2[grp];
+  const int c8 = (tid & 7) * 8;
+  const int r0 = tid >> 3;
+  uint32_t it = grp;
+  for (int b = blockIdx.x + grp * (int)gridDim.x; b < total; b += kGroups * (int)gridDim.x, it += kGroups) {
     const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
     const bool gave_up = !anc_ring::mbar_wait(full0 + 8 * slot, ph);
-    if (anc_ring::bar_compute_or(kThreads, gave_up)) {
+    if (anc_ring::bar_compute_or(1 + grp, kThreads, gave_up)) {
       if (gave_up && lane == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
       return;
     }
@@ -481,13 +492,13 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
     const uint16_t *sO = reinterpret_cast<const uint16_t *>(st + kRingHdr + kTileElems * 4);
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
-      anc_ring::ld8(reinterpret_cast<const float *>(st + kRingHdr) + k * (kThreads * 8), threadIdx.x, lane, pp[k]);
-      if (!w.tr) anc_ring::ld8_bf16(sO + k * (kThreads * 8), threadIdx.x, oo[k]);
+      anc_ring::ld8(reinterpret_cast<const float *>(st + kRingHdr) + k * (kThreads * 8), tid, lane, pp[k]);
+      if (!w.tr) anc_ring::ld8_bf16(sO + k * (kThreads * 8), tid, oo[k]);
     }
     if (w.tr) {
       // staged O^T tile (row oc = the weight tile's column oc) into the swizzled transposition tile
-      const int oc = threadIdx.x >> 2;
-      const int rr = (threadIdx.x & 3) * 16;
+      const int oc = tid >> 2;
+      const int rr = (tid & 3) * 16;
       const int sw = (lane >> 2) & 1;
       const uint4 *q = reinterpret_cast<const uint4 *>(sO + oc * kTile + rr);
       const uint4 a = q[sw], c = q[sw ^ 1];
@@ -497,7 +508,7 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
     __syncwarp();
     if (lane == 0) anc_ring::mbar_arrive(empty0 + 8 * slot);
     if (w.tr) {
-      anc_ring::bar_compute(kThreads);
+      anc_ring::bar_compute(1 + grp, kThreads);
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int rl = r0 + 32 * k;
@@ -505,7 +516,7 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
         for (int j = 0; j < 8; ++j) oo[k][j] = bf16_f32(sm[c8 + j][swz_col(c8 + j, rl)]);
       }
     }
-    const size_t flat0 = (size_t)t * kTileElems + (size_t)threadIdx.x * 8;
+    const size_t flat0 = (size_t)t * kTileElems + (size_t)tid * 8;
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const int rl = r0 + 32 * k;
@@ -905,13 +916,13 @@ static cudaError_t ring_kernels_ready(int device) {
   static bool done[64] = {};
   std::lock_guard<std::mutex> lock(mu);
   if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(momentum_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(momentum_ring_kernel<true, kMomGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)TileRing<8>::kSmemBytes);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(momentum_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(momentum_ring_kernel<false, kMomGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)TileRing<6>::kSmemBytes);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(update_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(update_ring_kernel<kUpdGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)TileRing<6>::kSmemBytes);
   if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
   return e;
@@ -945,11 +956,11 @@ int anc_launch_momentum_group(anc_ctx *ctx, const void *d_table, const anc_tmap 
   if (grid == 0) return ANC_OK;
   ANC_CUDA(ring_kernels_ready(ctx->device));
   if (grad_dtype == ANC_GRAD_F32)
-    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<true>, grid, kThreads + 32, TileRing<8>::kSmemBytes, st,
+    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<true, kMomGroups>, grid, kMomGroups * kThreads + 32, TileRing<8>::kSmemBytes, st,
                            (const MomW *)d_table, d_maps, xbase, n_w, tpw, momentum, nesterov, partial,
                            ctx->d_status));
   else
-    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<false>, grid, kThreads + 32, TileRing<6>::kSmemBytes, st,
+    ANC_CUDA(launch_pdl_ex(momentum_ring_kernel<false, kMomGroups>, grid, kMomGroups * kThreads + 32, TileRing<6>::kSmemBytes, st,
                            (const MomW *)d_table, d_maps, xbase, n_w, tpw, momentum, nesterov, partial,
                            ctx->d_status));
   return ANC_OK;
@@ -974,7 +985,7 @@ int anc_launch_update_group(anc_ctx *ctx, const void *d_table, const anc_tmap *d
   int grid = (int)(total < (long long)ctx->sm_count ? total : (long long)ctx->sm_count);   // one CTA per SM
   if (grid == 0) return ANC_OK;
   ANC_CUDA(ring_kernels_ready(ctx->device));
-  ANC_CUDA(launch_pdl_ex(update_ring_kernel, grid, kThreads + 32, TileRing<6>::kSmemBytes, st,
+  ANC_CUDA(launch_pdl_ex(update_ring_kernel<kUpdGroups>, grid, kUpdGroups * kThreads + 32, TileRing<6>::kSmemBytes, st,
                          (const UpdW *)d_table, d_maps, *omap, obase, n_w, tpw, lr_scale_wide, lr_scale_tall,
                          ctx->d_status));
   return ANC_OK;

@@ -68,22 +68,22 @@ __device__ __forceinline__ void box_load_3d(uint32_t dst, const void *map, int x
       "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
-// barrier among the first `count` threads of the CTA (the computing warps), id 1
-__device__ __forceinline__ void bar_compute(int count) {
-  asm volatile("bar.sync 1, %0;" ::"r"(count) : "memory");
+// barrier `id` (1, 2, ...) among the `count` threads of one group of computing warps
+__device__ __forceinline__ void bar_compute(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // The same barrier with an OR over a predicate: every computing warp learns whether any of them
 // gave up its wait, so that they leave together and nobody is left standing at a later barrier.
-__device__ __forceinline__ bool bar_compute_or(int count, bool pred) {
+__device__ __forceinline__ bool bar_compute_or(int id, int count, bool pred) {
   uint32_t r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %2, 0;\n\t"
-      "barrier.cta.red.or.pred q, 1, %1, p;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "barrier.cta.red.or.pred q, %1, %2, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(r)
-      : "r"(count), "r"((uint32_t)pred)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
       : "memory");
   return r != 0;
 }
