@@ -102,6 +102,7 @@ SIGNATURES = {
     "anc_muon_update": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "anc_ns_batched_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_f), _f, _i, _vp]),
     "anc_ns_chain_wait_selftest": (_i, [_vp, C.c_uint32]),
+    "anc_ring_wait_selftest": (_i, [_vp, C.c_uint32]),
     "anc_fro_normalize": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "anc_fro_normalize_static": (_i, [_i, _vp, _vp, _i, _i, _i, _f, _vp]),
     "anc_grad_accumulate": (_i, [_vp, _vp, _vp, _i, _vp, _u64, _u64, _f, _i, _u64, _u64, _i, _vp]),

@@ -73,6 +73,8 @@ int anc_launch_update(anc_ctx *ctx, float *p32, uint16_t *p16, const uint16_t *O
                       float lr_scale, int transposed, cudaStream_t st);
 int anc_launch_fro_normalize(anc_ctx *ctx, uint16_t *X, float *recip, int E, int M, int N, float eps,
                              cudaStream_t st);
+// Raises the shared-memory limit of the ring-fed sweeps on the context's device (idempotent).
+int anc_elem_kernels_prepare(anc_ctx *ctx);
 // Storage of one CUtensorMap (kept opaque here so that this header needs no driver types).
 struct alignas(64) anc_tmap { unsigned char b[128]; };
 // Tiled map over a dense row-major array of `slices` matrices of (rows, inner) elements of 2 or 4

@@ -538,6 +538,24 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
   }
 }
 
+// A stage nobody fills, waited for the way the ring's computing warps do: the bounded wait runs out, the
+// warps agree on it at their barrier, one of them records it and all return.
+__global__ void __launch_bounds__(kThreads)
+ring_wait_selftest_kernel(uint32_t tries, uint32_t *status) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t full = anc_ring::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    anc_ring::mbar_init(full, 1);
+    anc_ring::mbar_init_fence();
+  }
+  __syncthreads();
+  const bool gave_up = !anc_ring::mbar_wait(full, 0, tries);
+  if (anc_ring::bar_compute_or(1, kThreads, gave_up)) {
+    if (gave_up && (threadIdx.x & 31) == 0) atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+    return;
+  }
+}
+
 // ---- update with post-step consumers fused in ---------------------------------------------
 // Optional extra outputs of the update, produced from the freshly rounded bf16 weight while it is
 // still on chip (the reference runs them as separate sweeps after every optimizer step):
@@ -928,6 +946,12 @@ static cudaError_t ring_kernels_ready(int device) {
   return e;
 }
 
+// Called when a plan is created, so that the first step (which may run under stream capture) sets nothing.
+int anc_elem_kernels_prepare(anc_ctx *ctx) {
+  ANC_CUDA(ring_kernels_ready(ctx->device));
+  return ANC_OK;
+}
+
 int anc_launch_fro_finalize(anc_ctx *ctx, const float *partial, float *recip, int E, int per_matrix,
                             int warp_sums, float eps, uint32_t *sched, cudaStream_t st) {
   (void)ctx;
@@ -1009,6 +1033,16 @@ std::mutex g_static_mu;
 }  // namespace
 
 extern "C" {
+
+int anc_ring_wait_selftest(anc_ctx *ctx, uint32_t tries) {
+  ANC_REQUIRE(ctx, "ctx is NULL");
+  ANC_REQUIRE(tries > 0 && tries <= (1u << 20), "tries %u outside 1..2^20", tries);
+  anc_device_guard guard(ctx->device);
+  ring_wait_selftest_kernel<<<1, kThreads, 0, ctx->stream>>>(tries, ctx->d_status);
+  ANC_CUDA(cudaGetLastError());
+  ANC_CUDA(cudaStreamSynchronize(ctx->stream));
+  return ANC_OK;
+}
 
 int anc_muon_momentum(anc_ctx *ctx, float *buf, const void *g, int grad_dtype, uint16_t *u, int K,
                       int N, float momentum, int nesterov, int transposed, void *stream) {

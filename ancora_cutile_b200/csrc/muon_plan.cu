@@ -159,6 +159,13 @@ int anc_muon_plan_create_ex(anc_ctx *ctx, const anc_muon_weight *weights, const 
     }
     pl->outputs.push_back(o);
   }
+  {
+    int rc = anc_elem_kernels_prepare(ctx);
+    if (rc) {
+      plan_free(pl);
+      return rc;
+    }
+  }
   // scratch: sized for the largest batch over all groups
   size_t xe = 0, ae = 0, emax = 0;
   for (auto &g : pl->groups) {

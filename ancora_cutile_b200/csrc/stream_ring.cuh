@@ -43,8 +43,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kWaitTries; ++it)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t tries = kWaitTries) {
+  for (uint32_t it = 0; it < tries; ++it)
     if (mbar_try(bar, parity)) return true;
   return false;
 }

@@ -251,6 +251,11 @@ ANC_API int anc_muon_plan_last_timing(anc_muon_plan *plan, float ms[4], double n
  * kernel drains and returns, and status bit 0x10 is set in the context's status word; the
  * context stays usable.  Synchronises the context's stream. */
 ANC_API int anc_ns_chain_wait_selftest(anc_ctx *ctx, uint32_t spin_limit);
+/* No reference counterpart.  The same for the staging ring of the AdamW / momentum / update sweeps:
+ * one CTA waits, the way those kernels' computing warps do, for a stage nobody fills.  The wait gives
+ * up after `tries` polls (<= 2^20, each may suspend about 2 us), status bit 0x1 is set, the kernel
+ * returns and the context stays usable.  Synchronises the context's stream. */
+ANC_API int anc_ring_wait_selftest(anc_ctx *ctx, uint32_t tries);
 ANC_API int anc_muon_plan_scratch_bytes(anc_muon_plan *plan, uint64_t *bytes);
 ANC_API int anc_muon_plan_destroy(anc_muon_plan *plan);
 

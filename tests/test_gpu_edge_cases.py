@@ -106,3 +106,30 @@ def test_bad_arguments_raise(ctx):
     with pytest.raises(anc.AncoraError):
         K.ns_gemm_phase(0, d, None, d, 1, 100, 128, ctx=ctx)                                   # not a multiple of 128
     d.free()
+
+
+def test_ring_wait_runs_out_and_context_survives(ctx):
+    """A stage of the staging ring that nobody fills: the bounded wait gives up, the computing warps
+    agree on it and return, status bit 0x1 is set, and the context keeps working (no trap, no hang)."""
+    import ctypes as C
+    from ancora_cutile_b200 import _lib as L
+    ctx.sync()
+    assert ctx.status() == 0
+    L.check(L.lib().anc_ring_wait_selftest(ctx.handle, C.c_uint32(500)))
+    assert ctx.status() == 0x1
+    assert ctx.status() == 0                                       # reading clears it
+    with pytest.raises(anc.AncoraError):
+        L.check(L.lib().anc_ring_wait_selftest(ctx.handle, C.c_uint32(0)))
+    # ordinary work still runs: one AdamW step through the ring, bit-exact against the oracle
+    rng = np.random.default_rng(21)
+    n = 5000
+    p = rng.standard_normal(n).astype(np.float32)
+    g = (rng.standard_normal(n) * 1e-2).astype(np.float32)
+    opt = anc.AdamW({"w": p}, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, wd=0.01, ctx=ctx)
+    opt.step({"w": g}, ctx.stream)
+    ctx.sync()
+    z = np.zeros(n, np.float32)
+    want, _, _ = adamw_ref.adamw_update(p, z, z, g, adamw_ref.adamw_scalars(1e-3, 0.9, 0.95, 1e-8, 1), 0.01)
+    assert np.array_equal(opt.master()["w"].reshape(-1), want)
+    assert ctx.status() == 0
+    opt.free()
