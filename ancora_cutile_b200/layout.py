@@ -89,7 +89,11 @@ class ArenaLayout:
         by descending size (the last unit's exchange or copy-out is the one nothing overlaps,
         so the smallest goes last).  ``batch_cap[key]`` bounds a Muon unit by the scratch batch
         of the plan; ``max_elems`` cuts units into sub-ranges of at most that many elements (host
-        pipelining)."""
+        pipelining), and the sub-ranges of the last group then shrink toward the end (halves, down to
+        a quarter of ``max_elems``): what nothing overlaps in the pipelined round trip is the last
+        unit's compute and copy-out, so it is kept small, but not so small that the units' launches
+        fall behind their uploads.  How many units a rank's share is cut into never matters
+        to the exchange (``exchange_schedule``)."""
         units = []
         if max_elems is None:
             units.append(("adamw", self.a_begin, self.a_end))
@@ -97,14 +101,21 @@ class ArenaLayout:
             step = max(64, max_elems // 64 * 64)
             for lo in range(self.a_begin, self.a_end, step):
                 units.append(("adamw", lo, min(lo + step, self.a_end)))
-        for g in sorted(self.groups, key=lambda g: -g["total"]):
+        order = [g for g in sorted(self.groups, key=lambda g: -g["total"]) if g["names"][self.rank]]
+        for g in order:
             mine = len(g["names"][self.rank])
-            if not mine:
-                continue
             cap = mine if batch_cap is None else batch_cap[g["key"]]
             per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
-            for first in range(0, mine, per):
-                units.append(("muon", g["key"], first, min(per, mine - first)))
+            first = 0
+            while first < mine:
+                left = mine - first
+                count = min(per, left)
+                if max_elems is not None and g is order[-1] and left <= per:
+                    floor = max(1, max_elems // 4 // g["elems"])
+                    if left > floor:
+                        count = max(floor, (left + 1) // 2)
+                units.append(("muon", g["key"], first, count))
+                first += count
         return units
 
     def unit_span(self, unit):

@@ -124,8 +124,9 @@ class ResidentHybrid:
                 self._pgroup[(M, Nn)] = (gi, cap)
         # step_host cuts units to at most this many elements: its run time is the transfer time of
         # all bytes plus the (transfer + compute) time of the LARGEST unit, so smaller units shorten
-        # the pipeline's tail until the Newton-Schulz batches get too small to fill the GPU
-        self.host_chunk_elems = int(os.environ.get("ANCORA_HOST_CHUNK_ELEMS", 32 << 20))
+        # the pipeline's tail until the Newton-Schulz batches get too small to keep up with the uploads
+        # (measured on the benchmark step: 64 MiB units 27.5 ms, 32 MiB 26.8 ms, 16 MiB 38.8 ms)
+        self.host_chunk_elems = int(os.environ.get("ANCORA_HOST_CHUNK_ELEMS", 16 << 20))
         self._sub_plans = []
         self.units = self._make_units(None)
         self._host_units = None
@@ -458,13 +459,19 @@ class ResidentHybrid:
             self._host_units = self._make_units(self.host_chunk_elems)
 
     def _weight_views(self):
+        """{name: uint16 view of the page-locked weight arenas}; the arenas never move, so the views are
+        made once (a few hundred numpy slices per call would sit between two pipelined steps)."""
+        cached = getattr(self, "_wviews", None)
+        if cached is not None and cached[0] is self._pin_w:
+            return dict(cached[1])
         wa, wm = self._pin_w
         out = {}
         for n in self.adamw_names + self.muon_names:
             src = wa if n in self.a_off else wm
             o = self.a_off[n] if n in self.a_off else self.m_off[n]
             out[n] = src.array[o:o + _numel(self.shapes[n])].reshape(self.shapes[n])
-        return out
+        self._wviews = (self._pin_w, out)
+        return dict(out)
 
     def _comm_stream_handle(self):
         if self._comm_stream is None:

@@ -306,3 +306,26 @@ def test_routing_of_the_two_model_families():
             orders.append([w for op, w in sched if op == "gather"])
             assert [w for op, w in sched if op == "compute"] == list(range(len(units)))
         assert all(o == orders[0] for o in orders)
+
+
+def test_host_units_of_the_last_group_shrink_toward_the_end():
+    """Host pipelining: the last unit's compute and copy-out overlap nothing, so the last group's
+    sub-ranges halve down to a quarter of the chunk size; every owned matrix is still in exactly one unit
+    and the device-resident units (no max_elems) stay whole groups."""
+    q = S.qwen3_0_6b_shapes()
+    qm = muon_names_for(q)
+    for world in (1, 2, 4, 8):
+        for r in range(world):
+            lay = ArenaLayout(q, qm, r, world)
+            units = [u for u in lay.make_units(None, 32 << 20) if u[0] == "muon"]
+            last_key = units[-1][1]
+            per_key = {}
+            for _, key, first, count in units:
+                assert first == per_key.get(key, 0)              # contiguous, in order
+                per_key[key] = first + count
+            assert per_key == {g["key"]: len(g["names"][r]) for g in lay.groups if g["names"][r]}
+            tail = [u[3] for u in units if u[1] == last_key]
+            assert tail[-1] <= max(1, (32 << 20) // 4 // (last_key[0] * last_key[1])) or len(tail) == 1
+            assert all(a >= b for a, b in zip(tail, tail[1:]))
+            whole = [u for u in lay.make_units() if u[0] == "muon"]
+            assert len(whole) == len(per_key) and all(u[2] == 0 for u in whole)
