@@ -222,6 +222,7 @@ adamw_multi_kernel(const Chunk *__restrict__ chunks, uint32_t n_chunks, Scalars 
       const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
       if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
         atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        anc_ring::drain_issued<R::kStages>(full0, it);
         return;
       }
       uint8_t *st = ring + (size_t)slot * R::kStageBytes;

@@ -311,6 +311,7 @@ momentum_ring_kernel(const MomW *__restrict__ table, const anc_tmap *__restrict_
       const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
       if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
         atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        anc_ring::drain_issued<R::kStages>(full0, it);
         return;
       }
       const int tn = w.N / kTile, ti = t / tn, tj = t - ti * tn;
@@ -449,6 +450,7 @@ update_ring_kernel(const UpdW *__restrict__ table, const anc_tmap *__restrict__ 
       const uint32_t slot = it % R::kStages, ph = (it / R::kStages) & 1u;
       if (it >= (uint32_t)R::kStages && !anc_ring::mbar_wait(empty0 + 8 * slot, ph ^ 1u)) {
         atomicOr(status, ANC_DEV_TIMEOUT_TMA);
+        anc_ring::drain_issued<R::kStages>(full0, it);
         return;
       }
       const int tn = w.N / kTile, ti = t / tn, tj = t - ti * tn;

@@ -48,6 +48,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     if (mbar_try(bar, parity)) return true;
   return false;
 }
+// For the feeding thread when it gives up at iteration `it`: waits (bounded) until the copies of the
+// stages it issued last have landed, so that none is in flight when the CTA's shared memory is released.
+template <int kStages>
+__device__ __forceinline__ void drain_issued(uint32_t full0, uint32_t it) {
+  const uint32_t lo = it > (uint32_t)kStages ? it - (uint32_t)kStages : 0u;
+  for (uint32_t i = lo; i < it; ++i) mbar_wait(full0 + 8u * (i % kStages), (i / kStages) & 1u, 1u << 12);
+}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
