@@ -5,14 +5,20 @@ Pure host arithmetic (no device, no library): given the parameter shapes, the Mu
 
   AdamW arena : every tensor at a 64-element-aligned global offset, the arena padded to
                 world * per_rank; rank r owns the contiguous slice [r * per, (r + 1) * per).
-  Muon arena  : [shape group][owner rank][matrix]; inside a group every rank's region has the
+  Muon arena  : [arena group][owner rank][matrix]; inside a group every rank's region has the
                 same padded size ``per``, so a group is exchanged in place; the float32 state of
-                the owned matrices is packed [shape group][matrix] (``m_own_off``).
+                the owned matrices is packed [arena group][matrix] (``m_own_off``).  An arena group
+                is a shape group, except that with eight or more ranks the largest shape group is
+                cut into two parts (every rank's matrices of that shape, first half and second
+                half): the exchange of the first part then runs while the second is computed,
+                instead of the whole group's exchange starting when all of it is done.
 
 and cuts a step into units, each a contiguous span of this rank's share of one arena.  The
 reference keeps per-name buffers on one GPU (ancora/optim/adamw.py:76-87, optim/muon.py:236-254);
 arenas exist here so that one launch covers all tensors and one exchange covers a unit.
 """
+import os
+
 import numpy as np
 
 from .zero1 import partition_by_group, slice_bounds
@@ -50,29 +56,55 @@ class ArenaLayout:
         mshapes = [self.shapes[n] for n in self.muon_names]
         self.owner, self.load = partition_by_group(mshapes, W)
         self.m_owner = dict(zip(self.muon_names, self.owner))
-        self.groups = []                   # dicts: key, elems, per, base, names (by rank), own_base, total
+        self.groups = []      # dicts: key, shape, plan_first, elems, per, base, names (by rank), own_base, total
         self.m_off, self.m_own_off = {}, {}
         base = own = 0
-        for key in sorted({(min(s), max(s)) for s in mshapes}):
-            e = key[0] * key[1]
+        shape_keys = sorted({(min(s), max(s)) for s in mshapes})
+        members = {}
+        for key in shape_keys:
             by_rank = [[] for _ in range(W)]
             for n, r in zip(self.muon_names, self.owner):
                 if (min(self.shapes[n]), max(self.shapes[n])) == key:
                     by_rank[r].append(n)
-            per = max(len(x) for x in by_rank) * e
-            g = dict(key=key, elems=e, per=per, base=base, names=by_rank, own_base=own,
-                     total=sum(len(x) for x in by_rank) * e)
-            for r in range(W):
-                for k, n in enumerate(by_rank[r]):
-                    self.m_off[n] = base + r * per + k * e
-            for k, n in enumerate(by_rank[R]):
-                self.m_own_off[n] = own + k * e
-            base += W * per
-            own += len(by_rank[R]) * e
-            self.groups.append(g)
+            members[key] = by_rank
+        self.parts = self._parts(members)
+        for key in shape_keys:
+            e = key[0] * key[1]
+            whole = members[key]
+            k = self.parts[key]
+            cut = [[-(-len(x) * p // k) for p in range(k + 1)] for x in whole]     # per rank: part boundaries
+            for p in range(k):
+                by_rank = [x[c[p]:c[p + 1]] for x, c in zip(whole, cut)]
+                per = max(max(len(x) for x in by_rank), 1) * e
+                g = dict(key=key if p == 0 else key + (p,), shape=key, plan_first=cut[R][p], elems=e, per=per,
+                         base=base, names=by_rank, own_base=own, total=sum(len(x) for x in by_rank) * e)
+                for r in range(W):
+                    for j, n in enumerate(by_rank[r]):
+                        self.m_off[n] = base + r * per + j * e
+                for j, n in enumerate(by_rank[R]):
+                    self.m_own_off[n] = own + j * e
+                base += W * per
+                own += len(by_rank[R]) * e
+                self.groups.append(g)
         self.m_total = max(base, 64)
         self.m_owned_elems = own
         self.gmap = {g["key"]: g for g in self.groups}
+
+    def _parts(self, members):
+        """{shape key: number of arena groups the shape group is cut into}.  The same on every rank:
+        two for the largest shape group when there are at least eight ranks and every rank owns at
+        least eight of its matrices, else one.  ANCORA_GROUP_PARTS=k cuts the largest group into k
+        parts whatever the world size (for tests)."""
+        parts = {key: 1 for key in members}
+        if not members:
+            return parts
+        biggest = max(members, key=lambda k: (sum(len(x) for x in members[k]) * k[0] * k[1], k))
+        forced = int(os.environ.get("ANCORA_GROUP_PARTS", "0"))
+        if forced > 0:
+            parts[biggest] = forced
+        elif self.world >= 8 and min(len(x) for x in members[biggest]) >= 8:
+            parts[biggest] = 2
+        return parts
 
     def owned_range(self, name):
         """(start, stop) flat element range of ``name`` whose state this rank holds."""
@@ -85,7 +117,8 @@ class ArenaLayout:
 
     def make_units(self, batch_cap=None, max_elems=None):
         """Units in execution order: ("adamw", begin, end) over arena-0 elements, then
-        ("muon", group key, first, count) over this rank's matrices of each shape group, groups
+        ("muon", group key, first, count) over this rank's matrices of each arena group (``first``
+        counts inside the arena group; the group's ``plan_first`` places it inside the shape group), groups
         by descending size (the last unit's exchange or copy-out is the one nothing overlaps,
         so the smallest goes last).  ``batch_cap[key]`` bounds a Muon unit by the scratch batch
         of the plan; ``max_elems`` cuts units into sub-ranges of at most that many elements (host
@@ -104,7 +137,7 @@ class ArenaLayout:
         order = [g for g in sorted(self.groups, key=lambda g: -g["total"]) if g["names"][self.rank]]
         for g in order:
             mine = len(g["names"][self.rank])
-            cap = mine if batch_cap is None else batch_cap[g["key"]]
+            cap = mine if batch_cap is None else batch_cap[g["shape"]]
             per = cap if max_elems is None else max(1, min(cap, max_elems // g["elems"]))
             first = 0
             while first < mine:

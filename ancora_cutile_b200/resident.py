@@ -115,7 +115,8 @@ class ResidentHybrid:
         self.muon = MuonPlan(ws, grad_dtype=grad_dtype, max_batch=max_batch, ctx=c) if ws else None
         # Units of work, each a contiguous span of this rank's share of an arena:
         #   ("adamw", plan, begin, end)            arena-0 elements [begin, end)
-        #   ("muon", plan group, first, count)     matrices [first, first+count) of a shape group
+        #   ("muon", plan group, first, count, arena group key, first inside the arena group)
+        #                                          matrices [first, first+count) of a shape group of the plan
         self._gmap = lay.gmap
         self._pgroup = {}                      # shape key -> (plan group index, scratch batch)
         if self.muon is not None:
@@ -167,7 +168,8 @@ class ResidentHybrid:
         caps = {key: cap for key, (_, cap) in self._pgroup.items()}
         for u in self.layout.make_units(caps, max_elems):
             if u[0] == "muon":
-                units.append(("muon", self._pgroup[u[1]][0], u[2], u[3], u[1]))
+                g = self._gmap[u[1]]
+                units.append(("muon", self._pgroup[g["shape"]][0], g["plan_first"] + u[2], u[3], u[1], u[2]))
             elif max_elems is None:
                 units.append(("adamw", self.adamw, u[1], u[2]))
             else:                              # a sub-range of the slice gets a plan of its own
@@ -184,7 +186,7 @@ class ResidentHybrid:
         if unit[0] == "adamw":
             return 0, unit[2], unit[3] - unit[2]
         g = self._gmap[unit[4]]
-        return 1, g["base"] + self.rank * g["per"] + unit[2] * g["elems"], unit[3] * g["elems"]
+        return 1, g["base"] + self.rank * g["per"] + unit[5] * g["elems"], unit[3] * g["elems"]
 
     # ---------------------------------------------------------------- the step
     def _compute_unit(self, unit, si):

@@ -405,12 +405,12 @@ def main():
     adamw_gbs = 28.0 * a_owned / (adamw_ms / K * 1e-3) / 1e9 if adamw_ms > 0 else 0.0
     m_owned = eng.m_owned_elems
     elem_gbs = 24.0 * m_owned / ((mom_ms + upd_ms) / K * 1e-3) / 1e9 if (mom_ms + upd_ms) > 0 else 0.0
-    n_groups = len(eng.groups)
+    n_groups = len([g for g in eng.groups if g["names"][rank]])
     # DRAM traffic of the GEMM launches: algorithmic bytes per matrix and iteration are 6MN + 8M^2
     # (operands once, outputs once); the measured ratio of DRAM bytes to that comes from an ncu capture.
     gemm_kernel = "ns_chain_kernel" if os.environ.get("ANCORA_NS_CHAIN", "1") != "0" else "ns_gemm_pair_kernel"
     gemm_alg_bytes = sum(len(g["names"][rank]) * MUON_KW["ns_steps"] *
-                         (6 * g["key"][0] * g["key"][1] + 8 * g["key"][0] ** 2) for g in eng.groups)
+                         (6 * g["shape"][0] * g["shape"][1] + 8 * g["shape"][0] ** 2) for g in eng.groups)
     launches_per_step = max(gemm_launches // K, 1)
     out = {
         "metric": "hybrid_optimizer_step_params_per_s", "value": value, "unit": "params/s",

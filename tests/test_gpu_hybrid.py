@@ -103,6 +103,51 @@ def test_zero1_shards_bitwise_equal_single(ctx, world):
         assert covered[n] == int(np.prod(s)), n               # every element owned exactly once
 
 
+def test_group_parts_leave_the_bits_unchanged(ctx, monkeypatch):
+    """The largest shape group cut into two arena groups (what eight ranks do; forced here): the
+    whole model on one GPU, the four shards of a world of 4 and the pipelined host round trip all
+    give the bits of the uncut single-GPU step."""
+    shp = small_shapes()
+    params = S.synthetic_params(shp, seed=3)
+    mu = [n for n, p in params.items() if anc.default_is_muon(n, p)]
+    nd = tuple(n for n, s in shp.items() if len(s) == 1)
+    grads = S.synthetic_grads_bf16(shp, seed=4)
+
+    def run(rank, w, host=False):
+        eng = anc.ResidentHybrid(params, mu, nd, adamw_kw=AKW, grad_dtype="bf16", rounding="sr", seed=7,
+                                 rank=rank, world=w, schedule=anc.PE_SCHEDULE, ctx=ctx)
+        n_groups = len(eng.groups)
+        for _ in range(2):
+            if host:
+                eng.host_chunk_elems = 128 * 128 * 2
+                eng.step_host(grads, ctx.stream)
+            else:
+                eng.upload_grads(grads, ctx.stream)
+                eng.step(ctx.stream, exchange=False)
+        ctx.sync()
+        assert ctx.status() == 0
+        bits, _ = eng.download_weights_bits()
+        res = ({n: b.copy() for n, b in bits.items()}, eng.master(), {n: eng.owned_range(n) for n in shp}, n_groups)
+        eng.free()
+        return res
+
+    full_bits, full_master, _, g_plain = run(0, 1)
+    monkeypatch.setenv("ANCORA_GROUP_PARTS", "2")
+    for host in (False, True):
+        bits, master, _, g_cut = run(0, 1, host)
+        assert g_cut == g_plain + 1
+        for n in shp:
+            assert np.array_equal(bits[n], full_bits[n]), (host, n)
+            assert np.array_equal(master[n][2], full_master[n][2]), (host, n)
+    for r in range(4):
+        bits, master, owned, _ = run(r, 4)
+        for n in shp:
+            s, e = owned[n]
+            if e > s:
+                assert np.array_equal(bits[n].reshape(-1)[s:e], full_bits[n].reshape(-1)[s:e]), (r, n)
+                assert np.array_equal(master[n][2], full_master[n][2][s:e]), (r, n)
+
+
 def test_step_host_pipeline_equals_plain_step(ctx):
     """The pipelined host round trip (sub-chunked units on three streams) gives the same bits
     as upload + step + download, and its returned views are the updated parameters."""

@@ -47,8 +47,9 @@ def test_layout_is_the_same_on_every_rank_and_partitions_everything(which, world
     # Muon: every matrix inside its owner's region of its group, no two matrices overlap
     spans = []
     for n in mu:
-        g = a.gmap[(min(shp[n]), max(shp[n]))]
         r = a.m_owner[n]
+        g = next(g for g in a.groups if n in g["names"][r])
+        assert g["shape"] == (min(shp[n]), max(shp[n]))
         lo = g["base"] + r * g["per"]
         assert lo <= a.m_off[n] and a.m_off[n] + _numel(shp[n]) <= lo + g["per"], n
         spans.append((a.m_off[n], _numel(shp[n])))
@@ -329,3 +330,56 @@ def test_host_units_of_the_last_group_shrink_toward_the_end():
             assert all(a >= b for a, b in zip(tail, tail[1:]))
             whole = [u for u in lay.make_units() if u[0] == "muon"]
             assert len(whole) == len(per_key) and all(u[2] == 0 for u in whole)
+
+
+def test_the_largest_group_is_cut_in_two_from_eight_ranks_on():
+    """Arena groups: below eight ranks one per shape; at eight the largest shape group becomes two
+    arena groups (every rank's matrices of that shape, first and second half), each with its own
+    region and exchange; ``plan_first`` places a part inside the rank's matrices of the shape."""
+    for which in ("qwen3", "moe"):
+        shp, mu = _family(which)
+        for world in (1, 2, 4):
+            lay = ArenaLayout(shp, mu, 0, world)
+            assert set(lay.parts.values()) == {1} and all(g["key"] == g["shape"] for g in lay.groups)
+        lays = [ArenaLayout(shp, mu, r, 8) for r in range(8)]
+        big = max(lays[0].parts, key=lambda k: lays[0].parts[k])
+        assert lays[0].parts[big] == 2 and sum(lays[0].parts.values()) == len(lays[0].parts) + 1
+        assert all(l.parts == lays[0].parts for l in lays)
+        for r, lay in enumerate(lays):
+            halves = [g for g in lay.groups if g["shape"] == big]
+            assert [g["key"] for g in halves] == [big, big + (1,)]
+            n0, n1 = len(halves[0]["names"][r]), len(halves[1]["names"][r])
+            assert n0 - n1 in (0, 1) and halves[0]["plan_first"] == 0 and halves[1]["plan_first"] == n0
+            # the two parts' names, in order, are the rank's matrices of the shape in registration order
+            mine = [n for n in mu if lay.m_owner[n] == r and (min(shp[n]), max(shp[n])) == big]
+            assert halves[0]["names"][r] + halves[1]["names"][r] == mine
+            # owned state is packed [arena group][matrix]: part 1 follows part 0 directly
+            assert halves[1]["own_base"] == halves[0]["own_base"] + n0 * halves[0]["elems"]
+            # every rank enters the same gathers in the same order
+            units = lay.make_units()
+            sched = lay.exchange_schedule(["adamw" if u[0] == "adamw" else u[1] for u in units])
+            assert [w for op, w in sched if op == "gather"] == \
+                [w for op, w in lays[0].exchange_schedule(
+                    ["adamw" if u[0] == "adamw" else u[1] for u in lays[0].make_units()]) if op == "gather"]
+            assert sum(1 for op, w in sched if op == "gather") == 2 + len(lay.parts)
+
+
+def test_forced_parts_with_empty_shares(monkeypatch):
+    """ANCORA_GROUP_PARTS cuts the largest group whatever the world; a rank that owns one matrix of
+    it gets an empty second part, still has a region there and still enters that part's gather."""
+    monkeypatch.setenv("ANCORA_GROUP_PARTS", "2")
+    shp = {f"l{i}.w": (128, 256) for i in range(5)}
+    shp.update({f"l{i}.s": (128, 128) for i in range(2)})
+    mu = list(shp)
+    lays = [ArenaLayout(shp, mu, r, 4) for r in range(4)]
+    assert lays[0].parts == {(128, 128): 1, (128, 256): 2}
+    counts = [[len(g["names"][r]) for g in lays[r].groups if g["shape"] == (128, 256)] for r in range(4)]
+    assert sorted(map(tuple, counts)) == [(1, 0), (1, 0), (1, 0), (1, 1)]
+    orders = []
+    for r, lay in enumerate(lays):
+        units = lay.make_units()
+        sched = lay.exchange_schedule(["adamw" if u[0] == "adamw" else u[1] for u in units])
+        orders.append([w for op, w in sched if op == "gather"])
+        assert all(g["per"] >= g["elems"] for g in lay.groups)
+    assert all(o == orders[0] for o in orders)
+    assert sorted(map(str, orders[0])) == sorted(map(str, ["adamw", (128, 128), (128, 256), (128, 256, 1)]))
