@@ -8,7 +8,7 @@ Pure host arithmetic (no device, no library): given the parameter shapes, the Mu
   Muon arena  : [arena group][owner rank][matrix]; inside a group every rank's region has the
                 same padded size ``per``, so a group is exchanged in place; the float32 state of
                 the owned matrices is packed [arena group][matrix] (``m_own_off``).  An arena group
-                is a shape group, except that with eight or more ranks the largest shape group is
+                is a shape group, except that with four or more ranks the largest shape group is
                 cut into two parts (every rank's matrices of that shape, first half and second
                 half): the exchange of the first part then runs while the second is computed,
                 instead of the whole group's exchange starting when all of it is done.
@@ -92,8 +92,9 @@ class ArenaLayout:
 
     def _parts(self, members):
         """{shape key: number of arena groups the shape group is cut into}.  The same on every rank:
-        two for the largest shape group when there are at least eight ranks and every rank owns at
-        least eight of its matrices, else one.  ANCORA_GROUP_PARTS=k cuts the largest group into k
+        two for the largest shape group when there are at least four ranks and every rank owns at
+        least eight of its matrices, else one (measured on the benchmark step: 3.08 against 3.22 ms at
+        four ranks, no difference at two).  ANCORA_GROUP_PARTS=k cuts the largest group into k
         parts whatever the world size (for tests)."""
         parts = {key: 1 for key in members}
         if not members:
@@ -102,7 +103,7 @@ class ArenaLayout:
         forced = int(os.environ.get("ANCORA_GROUP_PARTS", "0"))
         if forced > 0:
             parts[biggest] = forced
-        elif self.world >= 8 and min(len(x) for x in members[biggest]) >= 8:
+        elif self.world >= 4 and min(len(x) for x in members[biggest]) >= 8:
             parts[biggest] = 2
         return parts
 

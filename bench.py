@@ -443,7 +443,7 @@ def main():
         "host_issue_ms_per_step": host_issue_ms,
         # per step: 3 GEMM launches per iteration and group, momentum + finalize + update per group, AdamW
         "gpu_launches": (gemm_launches // K) + 3 * n_groups + 1,
-        # arena groups of the Muon parameters = all-gathers per step besides AdamW's (from eight ranks on the
+        # arena groups of the Muon parameters = all-gathers per step besides AdamW's (from four ranks on the
         # largest shape group is two arena groups, exchanged one after the other)
         "muon_arena_groups": len(eng.groups),
         "state_bytes_per_gpu": eng.state_bytes() + (eng.muon.scratch_bytes() if eng.muon else 0),

@@ -332,15 +332,16 @@ def test_host_units_of_the_last_group_shrink_toward_the_end():
             assert len(whole) == len(per_key) and all(u[2] == 0 for u in whole)
 
 
-def test_the_largest_group_is_cut_in_two_from_eight_ranks_on():
-    """Arena groups: below eight ranks one per shape; at eight the largest shape group becomes two
+def test_the_largest_group_is_cut_in_two_from_four_ranks_on():
+    """Arena groups: below four ranks one per shape; from four on the largest shape group becomes two
     arena groups (every rank's matrices of that shape, first and second half), each with its own
     region and exchange; ``plan_first`` places a part inside the rank's matrices of the shape."""
     for which in ("qwen3", "moe"):
         shp, mu = _family(which)
-        for world in (1, 2, 4):
+        for world in (1, 2):
             lay = ArenaLayout(shp, mu, 0, world)
             assert set(lay.parts.values()) == {1} and all(g["key"] == g["shape"] for g in lay.groups)
+        assert sorted(ArenaLayout(shp, mu, 0, 4).parts.values())[-1] == 2
         lays = [ArenaLayout(shp, mu, r, 8) for r in range(8)]
         big = max(lays[0].parts, key=lambda k: lays[0].parts[k])
         assert lays[0].parts[big] == 2 and sum(lays[0].parts.values()) == len(lays[0].parts) + 1
