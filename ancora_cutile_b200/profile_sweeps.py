@@ -41,6 +41,8 @@ def main():
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--adamw-elems", type=int, default=155_648_000)
+    ap.add_argument("--adamw-zeros", action="store_true",
+                    help="AdamW gradients and moments all zero (embedding rows no token touched)")
     args = ap.parse_args()
     ctx = get_context()
     rng = np.random.default_rng(0)
@@ -58,8 +60,9 @@ def main():
     sched = muon_ns.PE_SCHEDULE
     na = args.adamw_elems // 2048 * 2048
     # seeded state, not zeros: IEEE division and square root take their slow paths on zero operands
-    aw = ResidentAdamW([dict(g=_arena(ctx, rng, na, np.uint16, 1e-3), p32=_arena(ctx, rng, na, np.float32, 0.02),
-                             m=_arena(ctx, rng, na, np.float32, 1e-4), v=_arena(ctx, rng, na, np.float32, 1e-6, True),
+    z = 0.0 if args.adamw_zeros else 1.0
+    aw = ResidentAdamW([dict(g=_arena(ctx, rng, na, np.uint16, 1e-3 * z), p32=_arena(ctx, rng, na, np.float32, 0.02),
+                             m=_arena(ctx, rng, na, np.float32, 1e-4 * z), v=_arena(ctx, rng, na, np.float32, 1e-6 * z, True),
                              p16=DBuf.zeros((na,), np.uint16, ctx), numel=na, wd=0.1)],
                        grad_dtype="bf16", rounding="sr", seed=1, ctx=ctx)
 

@@ -158,3 +158,37 @@ def test_sr_is_unbiased_and_deterministic(ctx):
     sr_err = abs(np.mean(outs) - master.mean())
     rne_err = abs(bits_to_f32(f32_to_bf16_bits(got[0][0])).astype(np.float64).mean() - master.mean())
     assert sr_err < rne_err / 20
+
+
+def test_zero_and_special_operands_bit_exact(ctx):
+    """Embedding rows no token touched (g = m = v = 0 for ever), signed zeros, denormals, infinities
+    and NaNs: the kernel steers zeros round the slow paths of the correctly rounded square root and
+    division, and must still produce the IEEE results of the reference's statements
+    (ancora/optim/adamw.py:34-37) bit for bit (NaNs compared as NaNs)."""
+    rng = np.random.default_rng(77)
+    n = 3 * 2048 + 37                                    # ring stages and a ragged tail
+    p, m, v, g = _state(rng, n)
+    m[:1500] = 0; v[:1500] = 0; g[:1500] = 0              # untouched rows
+    g[1500:1600] = -0.0; m[1500:1600] = 0; v[1500:1600] = 0
+    m[1600:1700] = -0.0; g[1600:1700] = 0                 # num = -0 with v > 0
+    v[1700:1720] = np.inf; g[1700:1720] = 0; m[1700:1720] = 0      # 0 / inf
+    v[1720:1740] = np.nan; g[1720:1740] = 0; m[1720:1740] = 0      # 0 / NaN = NaN
+    g[1740:1760] = np.nan
+    m[1760:1780] = np.inf
+    v[1780:1800] = np.float32(1e-42)                      # denormal second moment
+    g[1800:1820] = np.float32(1e-30)                      # g*g underflows to zero
+    v[1800:1820] = 0; m[1800:1820] = 0
+    v[-37:] = 0; m[-37:] = 0; g[-37:] = 0                 # the ragged tail (plain-load path) too
+    specs = [(p, m, v, g, 0.1)]
+    for grad_dtype in ("f32", "bf16"):
+        got, offs = _run(ctx, specs, grad_dtype, "rne", 0, 3)
+        with np.errstate(all="ignore"):
+            want = _oracle(specs, grad_dtype, "rne", 0, 3, offs)
+        for k in range(3):                               # p, m, v
+            a, b = got[0][k], want[0][k]
+            nan = np.isnan(b)
+            assert np.array_equal(np.isnan(a), nan), (grad_dtype, k)
+            assert np.array_equal(a[~nan].view(np.uint32), b[~nan].view(np.uint32)), (grad_dtype, k)
+        fin = ~np.isnan(want[0][0])
+        assert np.array_equal(got[0][3][fin], want[0][3][fin]), grad_dtype
+        assert fin.sum() > n - 200 and (~fin).sum() >= 40
