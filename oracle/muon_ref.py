@@ -73,7 +73,7 @@ def ns_bf16_chain(X16, steps=5, schedule=None, eps=1e-7, recip=None):
     matrix (scaled X, A, B', Y) is rounded to bf16; products accumulate in higher
     precision and the combines happen before the rounding (fused epilogues).  As on the
     device, the a*X term rides in the polynomial's diagonal: B' = b A + c A A + a I and
-    X' = B' X.  Tolerance-level model of the device result, used for error budgeting only."""
+    X' = B' X.  Tolerance-level model of the device result, used for error estimates only."""
     X = bits_f32(X16).astype(np.float32)
     if recip is None:
         recip = fro_recip(X, eps)
