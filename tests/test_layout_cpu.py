@@ -384,3 +384,68 @@ def test_forced_parts_with_empty_shares(monkeypatch):
         assert all(g["per"] >= g["elems"] for g in lay.groups)
     assert all(o == orders[0] for o in orders)
     assert sorted(map(str, orders[0])) == sorted(map(str, ["adamw", (128, 128), (128, 256), (128, 256, 1)]))
+
+
+def test_random_families_keep_the_layout_invariants():
+    """Seeded random shape families and world sizes (with and without a forced cut of the largest group):
+    arena groups tile the Muon arena, every matrix lies inside its owner's region of exactly one arena
+    group, a rank's units cover exactly its matrices with plan ranges that follow each other inside a
+    shape, and all ranks enter the same gathers in the same order."""
+    rng = np.random.default_rng(2024)
+    sides = [128, 256, 384, 512]
+    for trial in range(40):
+        world = int(rng.choice([1, 2, 3, 4, 8]))
+        n = int(rng.integers(1, 40))
+        shp = {}
+        for i in range(n):
+            k, m = int(rng.choice(sides)), int(rng.choice(sides))
+            shp[f"w{i}"] = (k, m)
+        shp["gain"] = (128,)
+        shp["embed"] = (int(rng.integers(1, 50)) * 64 + int(rng.integers(0, 64)), 128)
+        mu = [x for x in shp if x.startswith("w")]
+        forced = int(rng.choice([0, 0, 2, 3]))
+        if forced:
+            os.environ["ANCORA_GROUP_PARTS"] = str(forced)
+        try:
+            lays = [ArenaLayout(shp, mu, r, world) for r in range(world)]
+        finally:
+            os.environ.pop("ANCORA_GROUP_PARTS", None)
+        a = lays[0]
+        # arena groups tile [0, m_total) in order; the same on every rank
+        pos = 0
+        for g in a.groups:
+            assert g["base"] == pos and g["per"] % g["elems"] == 0 and g["per"] >= g["elems"]
+            pos += world * g["per"]
+        assert pos == a.m_total or (pos == 0 and a.m_total == 64)
+        for b in lays[1:]:
+            assert [(g["key"], g["base"], g["per"], g["names"]) for g in b.groups] == \
+                   [(g["key"], g["base"], g["per"], g["names"]) for g in a.groups]
+        seen = {}
+        for g in a.groups:
+            for r in range(world):
+                for j, name in enumerate(g["names"][r]):
+                    assert name not in seen and a.m_owner[name] == r
+                    assert (min(shp[name]), max(shp[name])) == g["shape"]
+                    assert a.m_off[name] == g["base"] + r * g["per"] + j * g["elems"]
+                    seen[name] = g["key"]
+        assert sorted(seen) == sorted(mu)
+        gathers = []
+        for r, lay in enumerate(lays):
+            units = lay.make_units(None, int(rng.choice([0, 1 << 16, 1 << 18])) or None)
+            nxt = {}
+            for u in units:
+                if u[0] != "muon":
+                    continue
+                g = lay.gmap[u[1]]
+                assert u[2] == nxt.get(u[1], 0) and u[3] >= 1
+                nxt[u[1]] = u[2] + u[3]
+            assert nxt == {g["key"]: len(g["names"][r]) for g in lay.groups if g["names"][r]}
+            # plan ranges of the parts of one shape follow each other
+            by_shape = {}
+            for g in lay.groups:
+                assert g["plan_first"] == by_shape.get(g["shape"], 0)
+                by_shape[g["shape"]] = g["plan_first"] + len(g["names"][r])
+            sched = lay.exchange_schedule(["adamw" if u[0] == "adamw" else u[1] for u in units])
+            assert [w for op, w in sched if op == "compute"] == list(range(len(units)))
+            gathers.append([w for op, w in sched if op == "gather"])
+        assert all(x == gathers[0] for x in gathers) and len(gathers[0]) == 1 + len(a.groups)
