@@ -21,6 +21,8 @@ before importing.  Only host (numpy) code of the reference is executed:
   ancora.optim.adamw._adamw kernel body,
   read from the source file and evaluated on
   float32 numpy arrays                        -> adamw.npz
+  the same statements on zeros, signed zeros, denormals, infinities and NaNs
+                                              -> adamw_special.npz
 
 The reference's AdamW runs only on a GPU (cuda.tile kernel) and has no host function to
 call.  Its arithmetic is four statements of plain operator syntax (adamw.py:34-37), so the
@@ -157,6 +159,31 @@ def main(ref_root):
                         hyper=np.array([lr, b1, b2, eps, wd, t], np.float64),
                         mn=env["mn"], vn=env["vn"], pn=env["pn"], p16=_bf16_bits(env["pn"]),
                         statements=np.array(body))
+    # 8. The same statements on special operands (rows no token touched: g = m = v = 0; signed zeros;
+    #    denormal, infinite and NaN moments and gradients)
+    n = 64
+    p = (ra.standard_normal(n) * 0.02).astype(f)
+    m = (ra.standard_normal(n) * 1e-4).astype(f)
+    v = np.abs(ra.standard_normal(n) * 1e-6).astype(f)
+    g = _bits_f32(_bf16_bits((ra.standard_normal(n) * 1e-3).astype(f))).astype(f)
+    g[0:8] = 0.0; m[0:8] = 0.0; v[0:8] = 0.0
+    g[8:16] = -0.0; m[8:16] = 0.0; v[8:16] = 0.0
+    m[16:24] = -0.0; g[16:24] = 0.0
+    v[24:28] = np.inf; g[24:28] = 0.0; m[24:28] = 0.0
+    v[28:32] = np.nan; g[28:32] = 0.0; m[28:32] = 0.0
+    g[32:36] = np.nan
+    m[36:40] = np.inf
+    v[40:44] = f(1e-42)
+    g[44:48] = f(1e-30); m[44:48] = 0.0; v[44:48] = 0.0
+    env = dict(ct=types.SimpleNamespace(sqrt=np.sqrt), g=g, tm=m, tv=v, tp=p,
+               beta1=f(b1), beta2=f(b2), eps=f(eps), lr=f(lr), wd=f(wd),
+               ibc1=f(1.0 / (1.0 - b1 ** t)), ibc2=f(1.0 / (1.0 - b2 ** t)))
+    with np.errstate(all="ignore"):
+        for stmt in body:
+            exec(stmt, env)
+    np.savez_compressed(os.path.join(HERE, "adamw_special.npz"), p=p, m=m, v=v, g=g,
+                        hyper=np.array([lr, b1, b2, eps, wd, t], np.float64),
+                        mn=env["mn"], vn=env["vn"], pn=env["pn"])
     print("wrote fixtures to", HERE)
 
 

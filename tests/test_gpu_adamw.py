@@ -192,3 +192,29 @@ def test_zero_and_special_operands_bit_exact(ctx):
         fin = ~np.isnan(want[0][0])
         assert np.array_equal(got[0][3][fin], want[0][3][fin]), grad_dtype
         assert fin.sum() > n - 200 and (~fin).sum() >= 40
+
+
+def test_special_operands_equal_the_reference_statements(ctx):
+    """The device kernel on the fixture recorded from the reference's own statements on special
+    operands (tests/golden/adamw_special.npz), float32 gradients, several copies of the 64 cases so that
+    they pass through a ring stage."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "adamw_special.npz"))
+    lr, b1, b2, eps, wd, t = z["hyper"]
+    rep = 40                                              # 2560 elements: one full stage and a part
+    tile = lambda a: np.tile(a, rep).astype(np.float32)
+    p, m, v, g = tile(z["p"]), tile(z["m"]), tile(z["v"]), tile(z["g"])
+    b = dict(g=anc.DBuf(g, ctx), p32=anc.DBuf(p, ctx), m=anc.DBuf(m, ctx), v=anc.DBuf(v, ctx),
+             p16=anc.DBuf.zeros(p.shape, np.uint16, ctx), numel=p.size, wd=float(wd))
+    opt = anc.ResidentAdamW([b], grad_dtype="f32", rounding="rne", ctx=ctx)
+    opt.step(None, lr=float(lr), b1=float(b1), b2=float(b2), eps=float(eps), t=int(t))
+    ctx.sync()
+    assert ctx.status() == 0
+    for name, buf in (("pn", b["p32"]), ("mn", b["m"]), ("vn", b["v"])):
+        got, want = buf.to_numpy(), tile(z[name])
+        nan = np.isnan(want)
+        assert np.array_equal(np.isnan(got), nan), name
+        assert np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32)), name
+    opt.free()
+    for k in ("g", "p32", "m", "v", "p16"):
+        b[k].free()

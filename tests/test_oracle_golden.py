@@ -135,6 +135,24 @@ def test_adamw_oracle_equals_the_reference_kernel_statements_bit_for_bit():
     assert np.array_equal(p16, z["p16"])
 
 
+def test_adamw_oracle_on_special_operands_equals_the_reference_statements():
+    """adamw_special.npz: the same four statements of the reference on rows no token touched
+    (g = m = v = 0), signed zeros, denormal / infinite / NaN moments and gradients.  Finite results and
+    zeros equal bit for bit (the sign of a zero included), NaNs are NaNs in the same places."""
+    z = np.load(os.path.join(G, "adamw_special.npz"))
+    lr, b1, b2, eps, wd, t = z["hyper"]
+    s = adamw_ref.adamw_scalars(lr, b1, b2, eps, int(t))
+    with np.errstate(all="ignore"):
+        pn, mn, vn, _ = adamw_ref.adamw_step(z["p"], z["m"], z["v"], z["g"], s, wd, "rne")
+    for name, got in (("mn", mn), ("vn", vn), ("pn", pn)):
+        want = z[name]
+        nan = np.isnan(want)
+        assert np.array_equal(np.isnan(got), nan), name
+        assert np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32)), name
+    assert np.isnan(z["pn"]).sum() == 8 and np.isinf(z["vn"]).sum() == 4 and np.isinf(z["pn"]).sum() == 4   # the cases are there
+    assert np.array_equal(z["pn"][:8].view(np.uint32), (z["p"][:8] - np.float32(lr) * (np.float32(wd) * z["p"][:8])).view(np.uint32))
+
+
 def test_adamw_scalars_definition():
     s = adamw_ref.adamw_scalars(3e-4, 0.9, 0.95, 1e-8, 10)
     assert s.omb1 == np.float32(1.0) - np.float32(0.9)          # float32 subtraction, adamw.py:34
