@@ -117,11 +117,14 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_two_gloo_ranks_exchange_complementary_spans():
+@pytest.mark.parametrize("parts", [0, 2])
+def test_two_gloo_ranks_exchange_complementary_spans(parts, monkeypatch):
     """What each rank would send in the exchange: the two ranks' AdamW spans tile the padded arena,
-    and inside every shape group rank r's span starts at base + r * per (the in-place all-gather's
-    slot) and holds exactly its matrices."""
+    and inside every arena group rank r's span starts at base + r * per (the in-place all-gather's
+    slot) and holds exactly its matrices; also with the largest shape group cut into two arena groups."""
     import torch.multiprocessing as mp
+    if parts:
+        monkeypatch.setenv("ANCORA_GROUP_PARTS", str(parts))      # the spawned ranks inherit it
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     port = 29500 + (os.getpid() % 2000)
@@ -133,6 +136,7 @@ def test_two_gloo_ranks_exchange_complementary_spans():
         p.join(60)
         assert p.exitcode == 0
     assert box[0]["groups"] == box[1]["groups"]
+    assert len(box[0]["groups"]) == 3 + (1 if parts else 0)
     a_spans = [(o, n) for b in box for (arena, o, n) in b["spans"] if arena == 0]
     assert _tiles(a_spans, 0, box[0]["a_padded"])
     shp, _ = _family("qwen3")
